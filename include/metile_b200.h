@@ -1,0 +1,121 @@
+/*
+ * C ABI of libmetile_b200.so: the MLX-format affine INT4 projection path for NVIDIA B200
+ * (sm_100a).  Plain pointers and sizes only; every pointer is DEVICE memory owned by the
+ * caller; the library allocates nothing, keeps no pointer after a call returns, and every
+ * call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream).
+ *
+ * Data layout (identical to what the reference project consumes, so packed MLX weights drop
+ * in unchanged -- metile/backends/mlx_quantized.py:478-480, kernels/affine_qmv.py:25-51):
+ *   x        bf16  [M, K]        row-major activations
+ *   w        u32   [N, K/8]      8 nibbles per word, element 8j+e in bits [4e, 4e+4)
+ *   scales   bf16  [N, K/64]     one per group of 64 along K
+ *   biases   bf16  [N, K/64]     w[n,k] = scales[n,k/64] * q[n,k] + biases[n,k/64]
+ *   out      bf16  [M, N]        y = x @ w^T, fp32 accumulation, one rounding at the store
+ *
+ * Return value: 0 (MT_OK) or a negative code; mt_status_string() names it.  Codes:
+ *   -1 shape, -2 alignment, -3 quantisation format, -4 CUDA launch error, -5 wrong device,
+ *   -6 null pointer, -7 workspace, -8 a bounded device-side wait gave up.
+ * Errors are detected before any GPU work is queued.  There is no CPU fallback.
+ *
+ * `flags`: 0 selects the kernel by row count (CUDA-core GEMV for M <= 2, tcgen05 MMA above).
+ *   MT_FLAG_FORCE_GEMV (1)   CUDA-core GEMV (M <= 8)
+ *   MT_FLAG_FORCE_UMMA (2)   tcgen05 path for any M (one accumulation order for every M:
+ *                            use it when rows must be bit-identical across batch sizes 1..128)
+ *   MT_FLAG_UMMA_SMEM_A (4)  tcgen05 path with the dequantised tile staged in shared memory
+ *                            instead of tensor memory
+ *   MT_FLAG_GELU (16)        mt_dense_act: x/(1+exp(-1.702x)) instead of SiLU
+ */
+#ifndef METILE_B200_H
+#define METILE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MT_FLAG_FORCE_GEMV 0x1u
+#define MT_FLAG_FORCE_UMMA 0x2u
+#define MT_FLAG_UMMA_SMEM_A 0x4u
+#define MT_FLAG_GELU 0x10u
+
+/* Library version (major*10000 + minor*100 + patch). */
+int mt_version(void);
+
+/* Human-readable name of a status code. */
+const char* mt_status_string(int status);
+
+/* 0 when the current CUDA device is compute capability 10.x, else MT_ERR_DEVICE. */
+int mt_device_check(void);
+
+/* Reads (and with reset != 0 clears) the device-side record of a bounded wait that gave up:
+ * words[0] = wait code (0 = none), [1] = block, [2] = thread, [3] = parity.  Synchronises the
+ * device.  Returns 0, or -8 when words[0] != 0. */
+int mt_device_status(unsigned int words[4], int reset);
+
+/* y = x @ dequant(w)^T (+ residual, added to the un-rounded sum).
+ * Replaces: metile/backends/mlx_quantized.py:691 (mlx_affine_qmv), :1538
+ * (mlx_affine_residual_qmv), kernels/affine_qmv.py:57,94 and, for M > 1,
+ * metile/backends/mlx_affine.py:359 (mlx_affine_matmul).  residual may be NULL. */
+int mt_affine_qmv(const void* x, const uint32_t* w, const void* scales, const void* biases,
+                  const void* residual, void* out, int M, int K, int N, int group_size, int bits,
+                  unsigned int flags, void* stream);
+
+/* out = silu(x @ Wg^T) * (x @ Wu^T) on un-rounded fp32 sums.
+ * Replaces: metile/backends/mlx_quantized.py:717 (mlx_affine_swiglu_qmv), :1645
+ * (mlx_affine_swiglu), kernels/affine_qmv.py:135,217. */
+int mt_affine_swiglu(const void* x, const uint32_t* gate_w, const void* gate_scales,
+                     const void* gate_biases, const uint32_t* up_w, const void* up_scales,
+                     const void* up_biases, void* out, int M, int K, int N, int group_size, int bits,
+                     unsigned int flags, void* stream);
+
+/* Bytes of device workspace mt_affine_mlp needs (the bf16 hidden activations [M, I]). */
+size_t mt_affine_mlp_workspace_bytes(int M, int H, int I);
+
+/* out[M,H] = down(swiglu(x)) + residual: gate/up [I, H/8], down [H, I/8].  `workspace` is
+ * caller-owned device memory of at least mt_affine_mlp_workspace_bytes() bytes, 16-byte
+ * aligned; its contents after the call are the bf16 hidden activations.
+ * Replaces: metile/backends/mlx_quantized.py:1770 (mlx_affine_mlp_executor) and the call in
+ * metile/integrations/mlx_lm.py:3837 (_execute_quantized_mlp).  residual may be NULL. */
+int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales,
+                  const void* gate_biases, const uint32_t* up_w, const void* up_scales,
+                  const void* up_biases, const uint32_t* down_w, const void* down_scales,
+                  const void* down_biases, const void* residual, void* workspace,
+                  size_t workspace_bytes, void* out, int M, int H, int I, int group_size, int bits,
+                  unsigned int flags, void* stream);
+
+/* sum_out = bf16(x + residual); norm_out = bf16(sum_out * rsqrt(mean((x+residual)^2) + eps) * w).
+ * Replaces: metile/backends/mlx.py:786 (mlx_add_rms_norm), kernels/add_rmsnorm.py:5.
+ * sum_out may be NULL. */
+int mt_add_rmsnorm(const void* x, const void* residual, const void* weight, void* sum_out,
+                   void* norm_out, int rows, int H, float eps, void* stream);
+
+/* out = bf16(x * rsqrt(mean(x^2) + eps) * w).
+ * Replaces: metile/backends/mlx.py:748 (mlx_rms_norm), kernels/rmsnorm.py:5. */
+int mt_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, float eps,
+               void* stream);
+
+/* Dense bf16 small-batch projection, w [N, K] bf16: out = bf16(bf16(x @ w^T) + residual).
+ * Every row is bit-identical to running it alone.  K % 128 == 0.  residual may be NULL.
+ * Replaces: metile/compiler/dense.py:302 (lower_dense_residual_qmv) and its backend entry
+ * metile/backends/mlx_dense_residual.py. */
+int mt_dense_rows(const void* x, const void* w, const void* residual, void* out, int M, int K,
+                  int N, void* stream);
+
+/* Dense bf16 small-batch SwiGLU with the typed epilogue of the reference's exact path.
+ * Replaces: metile/compiler/dense.py:193 (lower_dense_swiglu_qmv),
+ * metile/backends/mlx_dense_swiglu.py. */
+int mt_dense_swiglu(const void* x, const void* gate_w, const void* up_w, void* out, int M, int K,
+                    int N, void* stream);
+
+/* C[M,N] = act(A[M,K] @ B[K,N]), bf16, fp32 accumulate, M <= 128; act = SiLU, or the
+ * x/(1+exp(-1.702x)) GELU form with MT_FLAG_GELU.
+ * Replaces: kernels/mlp.py:34 (matmul_silu) and :7 (matmul_gelu). */
+int mt_dense_act(const void* a, const void* b, void* c, int M, int N, int K, unsigned int flags,
+                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* METILE_B200_H */

@@ -1,0 +1,301 @@
+"""MLX-format affine INT4 projections on CUDA, behind the reference's operator names.
+
+Reference surface reproduced (names, argument order, defaults, error behaviour):
+  metile/backends/mlx_quantized.py:691  mlx_affine_qmv
+  metile/backends/mlx_quantized.py:717  mlx_affine_swiglu_qmv
+  metile/backends/mlx_quantized.py:1538 mlx_affine_residual_qmv
+  metile/backends/mlx_quantized.py:1645 mlx_affine_swiglu
+  metile/backends/mlx_quantized.py:1723 mlx_affine_swiglu_executor
+  metile/backends/mlx_quantized.py:1770 mlx_affine_mlp_executor
+  metile/backends/mlx_quantized.py:754  repack_mlx_affine_weight
+
+Differences that are deliberate:
+  * activations are bfloat16 torch CUDA tensors; packed weights keep the MLX layout unchanged;
+  * there is no timing tournament: the kernel is chosen by row count (CUDA-core GEMV for up to
+    two rows, tcgen05 MMA above), so `autotune`, `block`, `outputs_per_simdgroup` and
+    `decode_dtype` are accepted for call-site compatibility and ignored;
+  * any number of rows is served from one read of the weights (the reference's scalar kernels
+    re-read them per row and its tuned residual path hands multi-row inputs to native MLX,
+    mlx_quantized.py:1569-1578);
+  * unsupported formats raise; nothing is rerouted to another implementation.
+"""
+
+from __future__ import annotations
+
+import contextlib
+import threading
+
+import torch
+
+from .. import _lib
+from ._common import (
+    check_affine_triple,
+    contiguous_2d,
+    library,
+    pointer,
+    require_cuda_bf16,
+    rows_of,
+    stream_pointer,
+)
+
+_state = threading.local()
+_dispatch_lock = threading.RLock()
+_swiglu_dispatches = {}
+_residual_dispatches = {}
+
+
+def _flags():
+    return getattr(_state, "flags", 0)
+
+
+@contextlib.contextmanager
+def batch_invariant(enabled=True):
+    """Serve every row count from the tcgen05 kernel family, so that a row's output bits do not
+    depend on whether it runs alone or in a batch of up to 128 (one accumulation order)."""
+    previous = _flags()
+    _state.flags = _lib.FLAG_FORCE_UMMA if enabled else 0
+    try:
+        yield
+    finally:
+        _state.flags = previous
+
+
+@contextlib.contextmanager
+def force_kernel(name):
+    """Pin the kernel family: "gemv", "umma" (A operand in tensor memory), "umma_smem" or None."""
+    table = {None: 0, "gemv": _lib.FLAG_FORCE_GEMV, "umma": _lib.FLAG_FORCE_UMMA,
+             "umma_smem": _lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A}
+    if name not in table:
+        raise ValueError(f"unknown kernel family {name!r}")
+    previous = _flags()
+    _state.flags = table[name]
+    try:
+        yield
+    finally:
+        _state.flags = previous
+
+
+def _algorithm(rows, flags):
+    if flags & _lib.FLAG_FORCE_GEMV:
+        return "gemv"
+    if flags & (_lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A):
+        return "umma_smem" if flags & _lib.FLAG_UMMA_SMEM_A else "umma"
+    return "gemv" if rows <= 2 else "umma"
+
+
+def _record(table, rows, input_features, output_features, dtype, group_size, bits, flags):
+    key = (rows, input_features, output_features, str(dtype), group_size, bits)
+    with _dispatch_lock:
+        table[key] = _algorithm(rows, flags)
+
+
+def _project(name, values, weight, scales, biases, residual, group_size, bits):
+    require_cuda_bf16(values, name)
+    output_features = check_affine_triple(name, values, weight, scales, biases, group_size, bits)
+    expected_shape = (*values.shape[:-1], output_features)
+    if residual is not None and (tuple(residual.shape) != expected_shape
+                                 or residual.dtype != values.dtype):
+        raise ValueError("residual must match the affine QMV output shape and dtype")
+    x = contiguous_2d(values)
+    res = None if residual is None else contiguous_2d(residual)
+    out = torch.empty((x.shape[0], output_features), dtype=values.dtype, device=values.device)
+    flags = _flags()
+    code = library().mt_affine_qmv(pointer(x), pointer(weight), pointer(scales), pointer(biases),
+                                   pointer(res), pointer(out), x.shape[0], x.shape[1],
+                                   output_features, group_size, bits, flags,
+                                   stream_pointer(values.device))
+    _lib.check(code, name)
+    return out.reshape(expected_shape), flags
+
+
+def mlx_affine_qmv(values, weight, scales, biases, *, group_size=64, bits=4, block=32,
+                   outputs_per_simdgroup=1, decode_dtype="f32"):
+    """y = values @ dequant(weight)^T for any number of rows."""
+    del block, outputs_per_simdgroup
+    if decode_dtype not in ("f32", "f16"):
+        raise ValueError("decode_dtype must be 'f32' or 'f16'")
+    out, _ = _project("affine QMV", values, weight, scales, biases, None, group_size, bits)
+    return out
+
+
+def mlx_affine_residual_qmv(values, weight, scales, biases, residual, *, group_size=64, bits=4,
+                            autotune=True):
+    """y = values @ dequant(weight)^T + residual, the residual added before the one rounding."""
+    del autotune
+    out, flags = _project("affine residual QMV", values, weight, scales, biases, residual,
+                          group_size, bits)
+    _record(_residual_dispatches, rows_of(values), values.shape[-1], weight.shape[0], values.dtype,
+            group_size, bits, flags)
+    return out
+
+
+def _swiglu(name, values, gate_weight, gate_scales, gate_biases, up_weight, up_scales, up_biases,
+            group_size, bits):
+    if not (bits == 4 and group_size == 64):
+        raise ValueError(f"{name} requires 4-bit group-64 weights")
+    if gate_biases is None or up_biases is None:
+        raise ValueError(f"{name} requires affine quantization biases")
+    require_cuda_bf16(values, name)
+    if (
+        values.dtype != gate_scales.dtype
+        or values.dtype != gate_biases.dtype
+        or gate_weight.shape != up_weight.shape
+        or gate_scales.shape != up_scales.shape
+        or gate_biases.shape != up_biases.shape
+    ):
+        raise ValueError(f"{name} requires matching gate/up weights and parameters")
+    output_features = check_affine_triple(name, values, gate_weight, gate_scales, gate_biases,
+                                          group_size, bits)
+    check_affine_triple(name, values, up_weight, up_scales, up_biases, group_size, bits)
+    x = contiguous_2d(values)
+    out = torch.empty((x.shape[0], output_features), dtype=values.dtype, device=values.device)
+    flags = _flags()
+    code = library().mt_affine_swiglu(pointer(x), pointer(gate_weight), pointer(gate_scales),
+                                      pointer(gate_biases), pointer(up_weight), pointer(up_scales),
+                                      pointer(up_biases), pointer(out), x.shape[0], x.shape[1],
+                                      output_features, group_size, bits, flags,
+                                      stream_pointer(values.device))
+    _lib.check(code, name)
+    _record(_swiglu_dispatches, x.shape[0], x.shape[1], output_features, values.dtype, group_size,
+            bits, flags)
+    return out.reshape(*values.shape[:-1], output_features)
+
+
+def mlx_affine_swiglu_qmv(values, gate_weight, gate_scales, gate_biases, up_weight, up_scales,
+                          up_biases, *, group_size=64, bits=4, block=32, outputs_per_simdgroup=1,
+                          decode_dtype="f32"):
+    """silu(values @ Wg^T) * (values @ Wu^T), SwiGLU applied to the un-rounded fp32 sums."""
+    del block, outputs_per_simdgroup, decode_dtype
+    return _swiglu("affine SwiGLU QMV", values, gate_weight, gate_scales, gate_biases, up_weight,
+                   up_scales, up_biases, group_size, bits)
+
+
+def mlx_affine_swiglu(values, gate_weight, gate_scales, gate_biases, up_weight, up_scales,
+                      up_biases, *, group_size=64, bits=4, autotune=True):
+    """Same computation as mlx_affine_swiglu_qmv; the reference's tuned dispatcher name."""
+    del autotune
+    return _swiglu("affine SwiGLU", values, gate_weight, gate_scales, gate_biases, up_weight,
+                   up_scales, up_biases, group_size, bits)
+
+
+def mlx_affine_swiglu_executor(sample_values, gate_weight, gate_scales, gate_biases, up_weight,
+                               up_scales, up_biases, *, group_size=64, bits=4):
+    """Validate once and return `execute(values)` bound to the weights."""
+    mlx_affine_swiglu(sample_values, gate_weight, gate_scales, gate_biases, up_weight, up_scales,
+                      up_biases, group_size=group_size, bits=bits)
+
+    def execute(values):
+        return _swiglu("affine SwiGLU", values, gate_weight, gate_scales, gate_biases, up_weight,
+                       up_scales, up_biases, group_size, bits)
+
+    return execute
+
+
+def mlx_affine_mlp_executor(sample_values, gate_weight, gate_scales, gate_biases, up_weight,
+                            up_scales, up_biases, down_weight, down_scales, down_biases,
+                            sample_residual, *, group_size=64, bits=4):
+    """Validate once and return `execute(values, residual)` = down(swiglu(values)) + residual.
+
+    One C-ABI call (mt_affine_mlp) runs both kernels back to back on the current stream; the
+    bf16 hidden activations live in a workspace tensor allocated per call.  Unlike the
+    reference (metile/backends/mlx_quantized.py:1806-1820) any row count is accepted and no
+    1-row call is needed first.
+    """
+    name = "affine MLP"
+    require_cuda_bf16(sample_values, name)
+    intermediate = check_affine_triple(name, sample_values, gate_weight, gate_scales, gate_biases,
+                                       group_size, bits)
+    check_affine_triple(name, sample_values, up_weight, up_scales, up_biases, group_size, bits)
+    if gate_weight.shape != up_weight.shape:
+        raise ValueError("affine MLP requires matching gate/up weights")
+    hidden_features = sample_values.shape[-1]
+    probe = torch.empty((1, intermediate), dtype=sample_values.dtype, device=sample_values.device)
+    if check_affine_triple(name, probe, down_weight, down_scales, down_biases, group_size,
+                           bits) != hidden_features:
+        raise ValueError("affine MLP down projection must map back to the input width")
+    if sample_residual is not None and (sample_residual.shape != sample_values.shape
+                                        or sample_residual.dtype != sample_values.dtype):
+        raise ValueError("residual must match the MLP output shape and dtype")
+    lib = library()
+    device = sample_values.device
+    pointers = [pointer(t) for t in (gate_weight, gate_scales, gate_biases, up_weight, up_scales,
+                                     up_biases, down_weight, down_scales, down_biases)]
+
+    def execute(values, residual=None):
+        if values.dtype != torch.bfloat16 or values.shape[-1] != hidden_features:
+            raise ValueError("affine MLP executor received activations of a different layout")
+        x = contiguous_2d(values)
+        res = None
+        if residual is not None:
+            if residual.shape != values.shape or residual.dtype != values.dtype:
+                raise ValueError("residual must match the MLP output shape and dtype")
+            res = contiguous_2d(residual)
+        rows = x.shape[0]
+        hidden = torch.empty((rows, intermediate), dtype=torch.bfloat16, device=device)
+        out = torch.empty((rows, hidden_features), dtype=torch.bfloat16, device=device)
+        code = lib.mt_affine_mlp(pointer(x), *pointers, pointer(res), pointer(hidden),
+                                 hidden.numel() * 2, pointer(out), rows, hidden_features,
+                                 intermediate, group_size, bits, _flags(), stream_pointer(device))
+        _lib.check(code, name)
+        return out.reshape(values.shape)
+
+    return execute
+
+
+def repack_mlx_affine_weight(weight, scales, biases):
+    """MLX output-major layout -> the reference's K-major layout (two nibbles per byte, even flat
+    index in the low nibble; scales and biases transposed).  Provided for callers that hold
+    K-major consumers; the CUDA kernels here read the MLX layout directly and never need it."""
+    if biases is None:
+        raise ValueError("native affine QMV requires affine biases")
+    if weight.ndim != 2 or scales.ndim != 2 or biases.shape != scales.shape:
+        raise ValueError("expected packed weight and matching two-dimensional parameters")
+    words = weight.to(torch.int64) & 0xFFFFFFFF
+    shifts = torch.arange(0, 32, 4, device=weight.device, dtype=torch.int64)
+    quantized = ((words[..., None] >> shifts) & 15).to(torch.uint8)
+    quantized = quantized.reshape(weight.shape[0], weight.shape[1] * 8).t().reshape(-1)
+    packed = quantized[0::2] | (quantized[1::2] << 4)
+    return packed, scales.t().contiguous(), biases.t().contiguous()
+
+
+def _dispatch_rows(table):
+    with _dispatch_lock:
+        items = sorted(table.items())
+    return tuple(
+        {
+            "rows": key[0],
+            "input_features": key[1],
+            "output_features": key[2],
+            "dtype": key[3],
+            "group_size": key[4],
+            "bits": key[5],
+            "algorithm": algorithm,
+            "implementation": "metile_b200",
+        }
+        for key, algorithm in items
+    )
+
+
+def mlx_affine_swiglu_dispatches():
+    """Which kernel family served each SwiGLU shape in this process."""
+    return _dispatch_rows(_swiglu_dispatches)
+
+
+def mlx_affine_residual_qmv_dispatches():
+    """Which kernel family served each residual projection shape in this process."""
+    return _dispatch_rows(_residual_dispatches)
+
+
+__all__ = [
+    "batch_invariant",
+    "force_kernel",
+    "mlx_affine_mlp_executor",
+    "mlx_affine_qmv",
+    "mlx_affine_residual_qmv",
+    "mlx_affine_residual_qmv_dispatches",
+    "mlx_affine_swiglu",
+    "mlx_affine_swiglu_dispatches",
+    "mlx_affine_swiglu_executor",
+    "mlx_affine_swiglu_qmv",
+    "repack_mlx_affine_weight",
+]

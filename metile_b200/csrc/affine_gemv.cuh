@@ -1,0 +1,261 @@
+// INT4 affine dequant-GEMV on the CUDA cores, for 1..8 activation rows served from ONE read of
+// the packed weights.
+//
+// Computes what the reference's kernels/affine_qmv.py:4-54 computes (word / element / group
+// indexing, w = scale*q + bias, fp32 accumulation, one rounding at the store) with the residual
+// epilogue of :124-131 and the SwiGLU epilogue of :204-208.  Unlike the reference's kernel, which
+// re-reads the weights once per activation row (flattened output index, :22-24), every row of the
+// batch shares the same weight registers here.
+//
+// Mapping: half a warp (16 lanes) owns one output row; lane l reads the 128-bit word group
+// j = l + 16*t of that row (32 nibbles = half a scale group), t = 0, 1, ...  A warp pass covers
+// 2*kRows output rows.  When N is small the K range of a row is cut into `ksplit` contiguous
+// parts handled by different warps of the CTA (more bytes in flight); the parts are summed
+// through shared memory in part order.  ksplit is a function of (N, K) only.  Nibbles are converted to fp32 without I2F: (w & mask) | 0x4B000000 is the
+// float 2^23 + 2^(4e)*q, and one FMA by 2^-4e with addend -2^(23-4e) yields q exactly.
+// Per 32-nibble slot the kernel accumulates dot = sum x*q and folds scale and bias once:
+// acc += scale*dot + bias*sum(x).  The order of every fp32 operation for one (row, output) pair
+// depends on K only -- not on the number of rows, the grid or N -- so results are bit-identical
+// for a row run alone or inside a batch of up to 8.
+#pragma once
+
+#include "common.cuh"
+
+namespace mt {
+
+__device__ __forceinline__ void decode_nibbles_f32(uint32_t w, float (&q)[8]) {
+    constexpr uint32_t kMagic = 0x4B000000u;  // 2^23
+    const uint32_t hi = w >> 12;
+    q[0] = __uint_as_float((w & 0x0000000Fu) | kMagic) - 8388608.0f;
+    q[1] = fmaf(__uint_as_float((w & 0x000000F0u) | kMagic), 0.0625f, -524288.0f);
+    q[2] = fmaf(__uint_as_float((w & 0x00000F00u) | kMagic), 0.00390625f, -32768.0f);
+    q[3] = fmaf(__uint_as_float((w & 0x0000F000u) | kMagic), 0.000244140625f, -2048.0f);
+    q[4] = fmaf(__uint_as_float((w & 0x000F0000u) | kMagic), 0.0000152587890625f, -128.0f);
+    q[5] = fmaf(__uint_as_float((hi & 0x00000F00u) | kMagic), 0.00390625f, -32768.0f);
+    q[6] = fmaf(__uint_as_float((hi & 0x0000F000u) | kMagic), 0.000244140625f, -2048.0f);
+    q[7] = fmaf(__uint_as_float((hi & 0x000F0000u) | kMagic), 0.0000152587890625f, -128.0f);
+}
+
+__device__ __forceinline__ uint4 ldg_stream_u4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+struct GemvWeights {
+    const uint32_t* w;
+    const uint16_t* scales;
+    const uint16_t* biases;
+};
+
+// kM rows of activations; kRows output rows per half-warp per pass; kDual = gate|up with SwiGLU.
+template <int kM, int kRows, bool kDual>
+__global__ void __launch_bounds__(256)
+affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeights second,
+                   const uint16_t* __restrict__ residual, uint16_t* __restrict__ out, int K, int N, int ksplit) {
+    constexpr int kStreams = kDual ? 2 : 1;
+    constexpr int kWarps = 8;
+    __shared__ float partial[kWarps][2][kStreams * kRows * kM];
+    const int lane = threadIdx.x & 31;
+    const int half = lane >> 4;
+    const int l16 = lane & 15;
+    const int warp = threadIdx.x >> 5;
+    const int part = warp % ksplit;          // which K part this warp sums
+    const int team = warp / ksplit;          // which row group of the CTA it belongs to
+    const int teams_per_cta = kWarps / ksplit;
+    const int slots_per_row = K >> 5;  // 128-bit word groups per weight row
+    const int words_per_row = K >> 3;
+    const int groups_per_row = K >> 6;
+    const int rows_per_pass = 2 * kRows;
+    const int slots_per_part = (slots_per_row + ksplit - 1) / ksplit;
+    const int slot_begin = part * slots_per_part;
+    const int slot_end = min(slot_begin + slots_per_part, slots_per_row);
+    const int team_global = blockIdx.x * teams_per_cta + team;
+    const int teams_total = gridDim.x * teams_per_cta;
+    // Every warp of a CTA runs the same number of passes (the bound depends on blockIdx only),
+    // so the __syncthreads below are reached by all of them.
+    const int passes = (N + teams_total * rows_per_pass - 1) / (teams_total * rows_per_pass);
+
+    for (int pass = 0; pass < passes; ++pass) {
+        const int row_base = (pass * teams_total + team_global) * rows_per_pass;
+        float acc[kStreams][kRows][kM];
+#pragma unroll
+        for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+            for (int r = 0; r < kRows; ++r)
+#pragma unroll
+                for (int m = 0; m < kM; ++m) acc[s][r][m] = 0.0f;
+
+        int rows[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int n = row_base + half * kRows + r;
+            rows[r] = n < N ? n : N - 1;  // clamp loads; the store is guarded
+        }
+
+        for (int slot = slot_begin + l16; slot < slot_end; slot += 16) {
+            uint4 packed[kStreams][kRows];
+            float scale[kStreams][kRows], bias[kStreams][kRows];
+#pragma unroll
+            for (int s = 0; s < kStreams; ++s) {
+                const GemvWeights& wt = s == 0 ? first : second;
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) {
+                    packed[s][r] = ldg_stream_u4(
+                        reinterpret_cast<const uint4*>(wt.w + (size_t)rows[r] * words_per_row) + slot);
+                    const size_t g = (size_t)rows[r] * groups_per_row + (slot >> 1);
+                    scale[s][r] = bf16_bits_to_f32(__ldg(wt.scales + g));
+                    bias[s][r] = bf16_bits_to_f32(__ldg(wt.biases + g));
+                }
+            }
+            float dot[kStreams][kRows][kM];
+            float xsum[kM];
+#pragma unroll
+            for (int m = 0; m < kM; ++m) {
+                xsum[m] = 0.0f;
+#pragma unroll
+                for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r) dot[s][r][m] = 0.0f;
+            }
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                float xv[kM][8];
+#pragma unroll
+                for (int m = 0; m < kM; ++m) {
+                    const uint4 raw =
+                        __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)slot * 32 + wi * 8));
+                    xv[m][0] = bf16_lo(raw.x); xv[m][1] = bf16_hi(raw.x);
+                    xv[m][2] = bf16_lo(raw.y); xv[m][3] = bf16_hi(raw.y);
+                    xv[m][4] = bf16_lo(raw.z); xv[m][5] = bf16_hi(raw.z);
+                    xv[m][6] = bf16_lo(raw.w); xv[m][7] = bf16_hi(raw.w);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) xsum[m] += xv[m][e];
+                }
+#pragma unroll
+                for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r) {
+                        const uint32_t word = wi == 0 ? packed[s][r].x
+                                            : wi == 1 ? packed[s][r].y
+                                            : wi == 2 ? packed[s][r].z
+                                                      : packed[s][r].w;
+                        float q[8];
+                        decode_nibbles_f32(word, q);
+#pragma unroll
+                        for (int m = 0; m < kM; ++m)
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) dot[s][r][m] = fmaf(q[e], xv[m][e], dot[s][r][m]);
+                    }
+            }
+#pragma unroll
+            for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+                for (int r = 0; r < kRows; ++r)
+#pragma unroll
+                    for (int m = 0; m < kM; ++m)
+                        acc[s][r][m] = fmaf(scale[s][r], dot[s][r][m], fmaf(bias[s][r], xsum[m], acc[s][r][m]));
+        }
+
+        // 16-lane butterfly inside each half-warp; every lane ends with the full sum.
+#pragma unroll
+        for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+            for (int r = 0; r < kRows; ++r)
+#pragma unroll
+                for (int m = 0; m < kM; ++m) {
+                    float v = acc[s][r][m];
+#pragma unroll
+                    for (int offset = 8; offset >= 1; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
+                    acc[s][r][m] = v;
+                }
+
+        if (ksplit > 1) {
+            if (l16 == 0) {
+#pragma unroll
+                for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+                        for (int m = 0; m < kM; ++m) partial[warp][half][(s * kRows + r) * kM + m] = acc[s][r][m];
+            }
+            __syncthreads();
+            if (part == 0 && l16 == 0) {
+#pragma unroll
+                for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+                        for (int m = 0; m < kM; ++m) {
+                            float v = acc[s][r][m];
+                            for (int p = 1; p < ksplit; ++p) v += partial[warp + p][half][(s * kRows + r) * kM + m];
+                            acc[s][r][m] = v;
+                        }
+            }
+            __syncthreads();
+        }
+
+        if (part == 0 && l16 == 0) {
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                const int n = row_base + half * kRows + r;
+                if (n < N) {
+#pragma unroll
+                    for (int m = 0; m < kM; ++m) {
+                        float v;
+                        if constexpr (kDual) v = swiglu_f32(acc[0][r][m], acc[kStreams - 1][r][m]);
+                        else v = acc[0][r][m];
+                        if (residual) v += bf16_bits_to_f32(residual[(size_t)m * N + n]);
+                        out[(size_t)m * N + n] = f32_to_bf16_bits(v);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// K parts per row: enough warps to keep the memory system busy when N is small.  Depends on
+// (N, K) only, never on the number of activation rows.
+inline int gemv_ksplit(int K, int N) {
+    int ksplit = 1;
+    const int slots = K >> 5;
+    while (ksplit < 8 && (long)N * ksplit < 16384 && slots / (ksplit * 2) >= 16) ksplit *= 2;
+    return ksplit;
+}
+
+template <int kM, bool kDual>
+inline int launch_gemv_m(const uint16_t* x, GemvWeights a, GemvWeights b, const uint16_t* residual, uint16_t* out,
+                         int K, int N, int sm_count, cudaStream_t stream) {
+    constexpr int kRows = kDual ? (kM <= 2 ? 2 : 1) : (kM <= 2 ? 4 : (kM <= 4 ? 2 : 1));
+    constexpr int kWarps = 8;
+    const int ksplit = gemv_ksplit(K, N);
+    const int rows_per_cta = (kWarps / ksplit) * 2 * kRows;
+    int grid = (N + rows_per_cta - 1) / rows_per_cta;
+    const int cap = sm_count * 16;
+    if (grid > cap) grid = cap;
+    affine_gemv_kernel<kM, kRows, kDual><<<grid, kWarps * 32, 0, stream>>>(x, a, b, residual, out, K, N, ksplit);
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
+}
+
+template <bool kDual>
+inline int launch_gemv(const void* x, GemvWeights a, GemvWeights b, const void* residual, void* out, int M, int K,
+                       int N, int sm_count, cudaStream_t stream) {
+    const uint16_t* xp = static_cast<const uint16_t*>(x);
+    const uint16_t* rp = static_cast<const uint16_t*>(residual);
+    uint16_t* op = static_cast<uint16_t*>(out);
+    switch (M) {
+        case 1: return launch_gemv_m<1, kDual>(xp, a, b, rp, op, K, N, sm_count, stream);
+        case 2: return launch_gemv_m<2, kDual>(xp, a, b, rp, op, K, N, sm_count, stream);
+        case 3: return launch_gemv_m<3, kDual>(xp, a, b, rp, op, K, N, sm_count, stream);
+        case 4: return launch_gemv_m<4, kDual>(xp, a, b, rp, op, K, N, sm_count, stream);
+        case 5: return launch_gemv_m<5, kDual>(xp, a, b, rp, op, K, N, sm_count, stream);
+        case 6: return launch_gemv_m<6, kDual>(xp, a, b, rp, op, K, N, sm_count, stream);
+        case 7: return launch_gemv_m<7, kDual>(xp, a, b, rp, op, K, N, sm_count, stream);
+        case 8: return launch_gemv_m<8, kDual>(xp, a, b, rp, op, K, N, sm_count, stream);
+        default: return MT_ERR_SHAPE;
+    }
+}
+
+}  // namespace mt

@@ -1,0 +1,259 @@
+// extern "C" entry points of libmetile_b200.so (declared in include/metile_b200.h).
+// One translation unit: the kernels live in the .cuh files included below.
+#include "../../include/metile_b200.h"
+
+#include "add_rmsnorm.cuh"
+#include "affine_gemv.cuh"
+#include "affine_umma.cuh"
+#include "common.cuh"
+#include "dense_rows.cuh"
+
+namespace mt {
+
+static int device_sm_count() {
+    static int cached[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (device < 64 && cached[device]) return cached[device];
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    if (device < 64) cached[device] = count;
+    return count;
+}
+
+static int device_is_sm100() {
+    static int cached[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (device < 64 && cached[device]) return cached[device] > 0;
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) return 0;
+    if (device < 64) cached[device] = major == 10 ? 1 : -1;
+    return major == 10;
+}
+
+static int check_format(int K, int N, int group_size, int bits) {
+    if (group_size != 64 || bits != 4) return MT_ERR_FORMAT;
+    if (K < 64 || K % 64 || N < 1) return MT_ERR_SHAPE;
+    return MT_OK;
+}
+
+static int check_affine_ptrs(const void* x, const uint32_t* w, const void* s, const void* b, const void* out) {
+    if (!x || !w || !s || !b || !out) return MT_ERR_NULL;
+    if (!aligned_to(x, 16) || !aligned_to(w, 16) || !aligned_to(s, 2) || !aligned_to(b, 2) || !aligned_to(out, 2))
+        return MT_ERR_ALIGN;
+    return MT_OK;
+}
+
+// Row-count split: the CUDA-core GEMV issues one FMA per weight per row, which stops hiding
+// behind HBM beyond two rows; from three rows on the tensor-core path is the faster one.
+static bool use_gemv(int M, unsigned int flags) {
+    if (flags & MT_FLAG_FORCE_GEMV) return true;
+    if (flags & (MT_FLAG_FORCE_UMMA | MT_FLAG_UMMA_SMEM_A)) return false;
+    return M <= 2;
+}
+
+static int run_projection(const void* x, const AffineWeights& first, const AffineWeights* second, const void* residual,
+                          void* out, int M, int K, int N, unsigned int flags, cudaStream_t stream) {
+    const int sms = device_sm_count();
+    if (sms <= 0) return MT_ERR_DEVICE;
+    if (M == 0) return MT_OK;
+    if (use_gemv(M, flags)) {
+        if (M > 8) return MT_ERR_SHAPE;
+        GemvWeights a{first.w, first.scales, first.biases};
+        GemvWeights b = second ? GemvWeights{second->w, second->scales, second->biases} : a;
+        return second ? launch_gemv<true>(x, a, b, residual, out, M, K, N, sms, stream)
+                      : launch_gemv<false>(x, a, b, residual, out, M, K, N, sms, stream);
+    }
+    const bool tmem_a = !(flags & MT_FLAG_UMMA_SMEM_A);
+    const uint16_t* xp = static_cast<const uint16_t*>(x);
+    const uint16_t* rp = static_cast<const uint16_t*>(residual);
+    uint16_t* op = static_cast<uint16_t*>(out);
+    for (int m0 = 0; m0 < M; m0 += 128) {
+        const int rows = M - m0 < 128 ? M - m0 : 128;
+        const int rc = launch_umma(xp + (size_t)m0 * K, &first, second, rp ? rp + (size_t)m0 * N : nullptr,
+                                   op + (size_t)m0 * N, rows, K, N, tmem_a, sms, stream);
+        if (rc != MT_OK) return rc;
+    }
+    return MT_OK;
+}
+
+// C[M,N] = act(A[M,K] @ B[K,N]); a thread owns two adjacent output columns of kRows rows.
+template <int kRows>
+__global__ void __launch_bounds__(128)
+dense_act_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, uint16_t* __restrict__ c, int M,
+                 int N, int K, int gelu) {
+    const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    const int m0 = blockIdx.y * kRows;
+    if (col >= N) return;
+    float acc[kRows][2];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) acc[r][0] = acc[r][1] = 0.0f;
+    const bool pair = col + 1 < N && (N % 2 == 0);
+    for (int k = 0; k < K; ++k) {
+        float b0, b1 = 0.0f;
+        if (pair) {
+            const uint32_t bv = __ldg(reinterpret_cast<const uint32_t*>(b + (size_t)k * N + col));
+            b0 = bf16_lo(bv);
+            b1 = bf16_hi(bv);
+        } else {
+            b0 = bf16_bits_to_f32(b[(size_t)k * N + col]);
+            if (col + 1 < N) b1 = bf16_bits_to_f32(b[(size_t)k * N + col + 1]);
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int m = m0 + r < M ? m0 + r : M - 1;
+            const float av = bf16_bits_to_f32(__ldg(a + (size_t)m * K + k));
+            acc[r][0] = fmaf(av, b0, acc[r][0]);
+            acc[r][1] = fmaf(av, b1, acc[r][1]);
+        }
+    }
+    const float slope = gelu ? 1.702f : 1.0f;
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        if (m0 + r >= M) break;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (col + j >= N) break;
+            const float v = acc[r][j];
+            c[(size_t)(m0 + r) * N + col + j] = f32_to_bf16_bits(v / (1.0f + __expf(-slope * v)));
+        }
+    }
+}
+
+}  // namespace mt
+
+using namespace mt;
+
+extern "C" {
+
+int mt_version(void) { return 100; }
+
+const char* mt_status_string(int status) {
+    switch (status) {
+        case MT_OK: return "ok";
+        case MT_ERR_SHAPE: return "unsupported shape";
+        case MT_ERR_ALIGN: return "misaligned pointer";
+        case MT_ERR_FORMAT: return "unsupported quantisation format (need 4 bits, group size 64)";
+        case MT_ERR_LAUNCH: return "CUDA launch error";
+        case MT_ERR_DEVICE: return "current device is not compute capability 10.x";
+        case MT_ERR_NULL: return "null pointer";
+        case MT_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case MT_ERR_DEVICE_WAIT: return "a bounded device-side wait gave up";
+        default: return "unknown status";
+    }
+}
+
+int mt_device_check(void) { return device_is_sm100() ? MT_OK : MT_ERR_DEVICE; }
+
+int mt_device_status(unsigned int words[4], int reset) {
+    if (!words) return MT_ERR_NULL;
+    if (cudaDeviceSynchronize() != cudaSuccess) return MT_ERR_LAUNCH;
+    if (cudaMemcpyFromSymbol(words, g_device_status, sizeof(unsigned int) * 4) != cudaSuccess) return MT_ERR_LAUNCH;
+    if (reset) {
+        const unsigned int zeros[4] = {0, 0, 0, 0};
+        if (cudaMemcpyToSymbol(g_device_status, zeros, sizeof(zeros)) != cudaSuccess) return MT_ERR_LAUNCH;
+    }
+    return words[0] ? MT_ERR_DEVICE_WAIT : MT_OK;
+}
+
+int mt_affine_qmv(const void* x, const uint32_t* w, const void* scales, const void* biases, const void* residual,
+                  void* out, int M, int K, int N, int group_size, int bits, unsigned int flags, void* stream) {
+    int rc = check_format(K, N, group_size, bits);
+    if (rc != MT_OK) return rc;
+    if (M < 0) return MT_ERR_SHAPE;
+    if (M == 0) return MT_OK;
+    rc = check_affine_ptrs(x, w, scales, biases, out);
+    if (rc != MT_OK) return rc;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    AffineWeights first{w, static_cast<const uint16_t*>(scales), static_cast<const uint16_t*>(biases)};
+    return run_projection(x, first, nullptr, residual, out, M, K, N, flags, static_cast<cudaStream_t>(stream));
+}
+
+int mt_affine_swiglu(const void* x, const uint32_t* gate_w, const void* gate_scales, const void* gate_biases,
+                     const uint32_t* up_w, const void* up_scales, const void* up_biases, void* out, int M, int K,
+                     int N, int group_size, int bits, unsigned int flags, void* stream) {
+    int rc = check_format(K, N, group_size, bits);
+    if (rc != MT_OK) return rc;
+    if (M < 0) return MT_ERR_SHAPE;
+    if (M == 0) return MT_OK;
+    rc = check_affine_ptrs(x, gate_w, gate_scales, gate_biases, out);
+    if (rc != MT_OK) return rc;
+    rc = check_affine_ptrs(x, up_w, up_scales, up_biases, out);
+    if (rc != MT_OK) return rc;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    AffineWeights gate{gate_w, static_cast<const uint16_t*>(gate_scales), static_cast<const uint16_t*>(gate_biases)};
+    AffineWeights up{up_w, static_cast<const uint16_t*>(up_scales), static_cast<const uint16_t*>(up_biases)};
+    return run_projection(x, gate, &up, nullptr, out, M, K, N, flags, static_cast<cudaStream_t>(stream));
+}
+
+size_t mt_affine_mlp_workspace_bytes(int M, int H, int I) {
+    (void)H;
+    if (M <= 0 || I <= 0) return 0;
+    return (size_t)M * (size_t)I * 2;
+}
+
+int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales, const void* gate_biases,
+                  const uint32_t* up_w, const void* up_scales, const void* up_biases, const uint32_t* down_w,
+                  const void* down_scales, const void* down_biases, const void* residual, void* workspace,
+                  size_t workspace_bytes, void* out, int M, int H, int I, int group_size, int bits,
+                  unsigned int flags, void* stream) {
+    int rc = check_format(H, I, group_size, bits);
+    if (rc != MT_OK) return rc;
+    rc = check_format(I, H, group_size, bits);
+    if (rc != MT_OK) return rc;
+    if (M < 0) return MT_ERR_SHAPE;
+    if (M == 0) return MT_OK;
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < mt_affine_mlp_workspace_bytes(M, H, I))
+        return MT_ERR_WORKSPACE;
+    rc = mt_affine_swiglu(x, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, workspace, M, H, I,
+                          group_size, bits, flags, stream);
+    if (rc != MT_OK) return rc;
+    return mt_affine_qmv(workspace, down_w, down_scales, down_biases, residual, out, M, I, H, group_size, bits, flags,
+                         stream);
+}
+
+int mt_add_rmsnorm(const void* x, const void* residual, const void* weight, void* sum_out, void* norm_out, int rows,
+                   int H, float eps, void* stream) {
+    if (!residual) return MT_ERR_NULL;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    return launch_add_rmsnorm(x, residual, weight, sum_out, norm_out, rows, H, eps, static_cast<cudaStream_t>(stream));
+}
+
+int mt_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, float eps, void* stream) {
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    return launch_add_rmsnorm(x, nullptr, weight, nullptr, out, rows, H, eps, static_cast<cudaStream_t>(stream));
+}
+
+int mt_dense_rows(const void* x, const void* w, const void* residual, void* out, int M, int K, int N, void* stream) {
+    if (!x || !w || !out) return MT_ERR_NULL;
+    if (M == 0) return MT_OK;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    return launch_dense<DenseEpilogue::kPlain>(x, w, nullptr, residual, out, M, K, N, device_sm_count(),
+                                               static_cast<cudaStream_t>(stream));
+}
+
+int mt_dense_swiglu(const void* x, const void* gate_w, const void* up_w, void* out, int M, int K, int N,
+                    void* stream) {
+    if (!x || !gate_w || !up_w || !out) return MT_ERR_NULL;
+    if (M == 0) return MT_OK;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    return launch_dense<DenseEpilogue::kSwiglu>(x, gate_w, up_w, nullptr, out, M, K, N, device_sm_count(),
+                                                static_cast<cudaStream_t>(stream));
+}
+
+int mt_dense_act(const void* a, const void* b, void* c, int M, int N, int K, unsigned int flags, void* stream) {
+    if (!a || !b || !c) return MT_ERR_NULL;
+    if (M < 0 || M > 128 || N < 1 || K < 1) return MT_ERR_SHAPE;
+    if (M == 0) return MT_OK;
+    if (!aligned_to(b, 4)) return MT_ERR_ALIGN;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    constexpr int kRows = 8;
+    dim3 grid(((N + 1) / 2 + 127) / 128, (M + kRows - 1) / kRows);
+    dense_act_kernel<kRows><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(a), static_cast<const uint16_t*>(b), static_cast<uint16_t*>(c), M, N, K,
+        (flags & MT_FLAG_GELU) ? 1 : 0);
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
+}
+
+}  // extern "C"
