@@ -1,0 +1,432 @@
+"""Benchmark of the INT4 fused SwiGLU MLP path (BASELINE config 1: Llama-3.2-1B shape,
+hidden 2048 / intermediate 8192, group 64, rows M in {1,2,4,8,16,32,128}).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one sweep: the fused MLP (gate|up SwiGLU -> down + residual) once for every M of
+the sweep, each call on the next of a rotating set of weight copies larger than L2.  `value` is
+the weight bytes streamed per second over the whole step with all inputs resident in HBM (the
+sweep replayed as a CUDA graph); `e2e` is the same metric through the public executor with HOST
+activations (pinned), host->device and device->host copies inside the timed region.  The JSON
+line also carries per-M times, the roofline of the dominant kernel, and a CPU baseline.
+
+With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) the workload is the
+tensor-parallel MLP of BASELINE config 4 (hidden 5120 / intermediate 27648): gate|up
+column-sharded, down row-sharded, one NCCL all-reduce per MLP; scaling is "strong".
+
+--impl reference times the reference semantics on the host cores (the C + OpenMP port under
+oracle/, because MLX itself cannot be installed here) on the same workload and prints the same
+line shape with "impl": "reference".
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SWEEP = (1, 2, 4, 8, 16, 32, 128)
+HIDDEN, INTERMEDIATE = 2048, 8192
+TP_HIDDEN, TP_INTERMEDIATE = 5120, 27648
+TP_SWEEP = (1, 16, 128)
+NOMINAL_HBM_GBS = 8000.0
+
+
+def weight_bytes(hidden, intermediate):
+    """Packed nibbles + bf16 scale and bias per group of 64, three projections."""
+    per_weight = 0.5 + 2 * 2 / 64
+    return int(3 * hidden * intermediate * per_weight)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            data = json.load(handle)
+        return float(data["hbm_gbs"]), float(data.get("bf16_tflops_sustained", 1420.5)), "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                fields = [f.strip() for f in out.strip().splitlines()[0].split(",")]
+                self.samples.append(float(fields[0]))
+                self.max_mhz = float(fields[1])
+                for name, value in zip(names, fields[2:6]):
+                    if value.lower().startswith("active"):
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def bits_triple(triple):
+    from metile_b200 import synth
+
+    return triple[0].cpu().numpy(), synth.to_numpy_bits(triple[1]), synth.to_numpy_bits(triple[2])
+
+
+def cpu_sweep_seconds(hidden, intermediate, sweep, repeats):
+    """Time the C + OpenMP port of the reference semantics on the host cores."""
+    from metile_b200 import synth
+    from oracle import cport
+
+    gate, up, down = synth.mlp_weights(100, hidden, intermediate)
+    triples = [bits_triple(t) for t in (gate, up, down)]
+    inputs = [(synth.to_numpy_bits(synth.activations(5, m, hidden)),
+               synth.to_numpy_bits(synth.activations(6, m, hidden))) for m in sweep]
+    cport.mlp(inputs[0][0], *triples, inputs[0][1])  # warm-up (thread pool, page faults)
+    times = []
+    for _ in range(repeats):
+        start = time.perf_counter()
+        for x, r in inputs:
+            cport.mlp(x, *triples, r)
+        times.append(time.perf_counter() - start)
+    return times, cport.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tp = args.gpus > 1
+    hidden, inter, sweep = (TP_HIDDEN, TP_INTERMEDIATE, TP_SWEEP) if tp else (HIDDEN, INTERMEDIATE, SWEEP)
+    total_bytes = weight_bytes(hidden, inter) * len(sweep)
+    times, cores = cpu_sweep_seconds(hidden, inter, sweep, args.warmup + args.steps)
+    timed = times[args.warmup:]
+    seconds = sum(timed) / len(timed)
+    value = total_bytes / seconds / 1e9
+    line = {
+        "impl": "reference",
+        "metric": "int4_fused_mlp_weight_GBps",
+        "value": value,
+        "unit": "GB/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": seconds * 1e3,
+        "higher_is_better": True,
+        "scaling": "strong" if tp else "weak",
+        "vs_baseline": None,
+        "dtype": "bf16 activations, u4 weights, fp32 accumulate",
+        "data": "synthetic",
+        "config": workload_config(hidden, inter, sweep, args.gpus, "host memory (CPU run)"),
+        "tokens_per_s": sum(sweep) / seconds,
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{len(timed)} full sweeps M={list(sweep)} of the same MLP"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "MLX-CPU (the reference's own CPU path) is unavailable on this box; this is the C + OpenMP "
+                "port of its semantics under oracle/",
+    }
+    print(json.dumps(line))
+
+
+def workload_config(hidden, inter, sweep, gpus, l2_note):
+    return {
+        "workload": ("int4_swiglu_mlp_llama3.2-1b" if hidden == HIDDEN else "int4_swiglu_mlp_qwen2.5-32b_tp"),
+        "hidden": hidden,
+        "intermediate": inter,
+        "group_size": 64,
+        "bits": 4,
+        "rows_sweep": list(sweep),
+        "weight_bytes_per_mlp": weight_bytes(hidden, inter),
+        "parallelism": "single GPU" if gpus == 1 else f"tp{gpus} (gate|up column-sharded, down row-sharded, 1 all-reduce)",
+        "l2": l2_note,
+    }
+
+
+def run_ours(args):
+    import torch
+
+    from metile_b200 import backends as B
+    from metile_b200 import synth
+    from metile_b200 import tp as tensor_parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    tp = distributed
+    hidden, inter, sweep = (TP_HIDDEN, TP_INTERMEDIATE, TP_SWEEP) if tp else (HIDDEN, INTERMEDIATE, SWEEP)
+    per_mlp_bytes = weight_bytes(hidden, inter)
+    local_bytes = per_mlp_bytes // world
+    l2_bytes = torch.cuda.get_device_properties(device).L2_cache_size
+    copies = max(2, -(-2 * l2_bytes // local_bytes) + 1)
+    copies = min(copies, 24)
+
+    # ---- build the rotating weight sets and executors -------------------------------------------
+    executors = []
+    for c in range(copies):
+        if tp:
+            executors.append(tensor_parallel.TensorParallelMLP.from_seed(100, hidden, inter, device, rank, world))
+        else:
+            gate, up, down = synth.mlp_weights(100, hidden, inter, device)
+            sample = synth.activations(5, 1, hidden, device)
+            executors.append(B.mlx_affine_mlp_executor(sample, *gate, *up, *down, sample))
+    inputs = {m: (synth.activations(5, m, hidden, device), synth.activations(6, m, hidden, device)) for m in sweep}
+    host_inputs = {m: (inputs[m][0].cpu().pin_memory(), inputs[m][1].cpu().pin_memory()) for m in sweep}
+    host_outputs = {m: torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory() for m in sweep}
+    cursor = [0]
+
+    def next_executor():
+        cursor[0] = (cursor[0] + 1) % copies
+        return executors[cursor[0]]
+
+    def sweep_once():
+        for m in sweep:
+            x, r = inputs[m]
+            next_executor()(x, r)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream()
+
+    def capture(fn, repeats):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(repeats):
+                    fn()
+        torch.cuda.synchronize()
+        return graph
+
+    def time_graph(graph, replays):
+        with torch.cuda.stream(stream):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            for _ in range(replays):
+                graph.replay()
+            stop.record(stream)
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) * 1e-3
+
+    # ---- headline: K steps, each one sweep, replayed as a CUDA graph ------------------------------
+    for _ in range(3):
+        sweep_once()
+    torch.cuda.synchronize()
+    step_graph = capture(sweep_once, 1)
+    for _ in range(max(args.warmup, 3)):
+        step_graph.replay()
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        seconds = time_graph(step_graph, args.steps)
+        barrier()
+        # Keep the sampler alive long enough for a few samples when the steps are very short.
+        if seconds < 1.0:
+            filler = time_graph(step_graph, max(1, int(1.0 / max(seconds / args.steps, 1e-6))))
+            del filler
+    if distributed:
+        t = torch.tensor([seconds], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        seconds = float(t.item())
+    step_seconds = seconds / args.steps
+    total_bytes = per_mlp_bytes * len(sweep)
+    value = total_bytes / step_seconds / 1e9
+
+    # ---- per-M detail (graph of 8 MLP calls per M) ------------------------------------------------
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    detail = []
+    for m in sweep:
+        x, r = inputs[m]
+
+        def one(x=x, r=r):
+            next_executor()(x, r)
+
+        graph = capture(one, 8)
+        graph.replay()
+        barrier()
+        per_call = time_graph(graph, 10) / 80
+        if distributed:
+            t = torch.tensor([per_call], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            per_call = float(t.item())
+        flops = 2.0 * 3 * hidden * inter * m
+        hbm_seconds = (local_bytes) / (hbm_peak * 1e9)
+        tensor_seconds = flops / world / (tensor_peak * 1e12)
+        detail.append({
+            "rows": m,
+            "us": per_call * 1e6,
+            "weight_GBps": per_mlp_bytes / per_call / 1e9,
+            "tokens_per_s": m / per_call,
+            "frac_of_hbm": (local_bytes / per_call / 1e9) / hbm_peak,
+            "frac_of_nominal_8TBps": (local_bytes / per_call / 1e9) / NOMINAL_HBM_GBS,
+            "bound": "hbm" if hbm_seconds >= tensor_seconds else "tensor",
+            "frac_of_roofline": max(hbm_seconds, tensor_seconds) / per_call,
+        })
+
+    # ---- roofline of the dominant kernel: gate|up SwiGLU at M=1, timed alone ----------------------
+    roofline = None
+    if not tp:
+        gate_sets = [synth.mlp_weights(100, hidden, inter, device)[:2] for _ in range(copies)]
+        x1 = inputs[sweep[0]][0]
+        gate_cursor = [0]
+
+        def gate_up():
+            gate_cursor[0] = (gate_cursor[0] + 1) % copies
+            gate, up = gate_sets[gate_cursor[0]]
+            B.mlx_affine_swiglu(x1, *gate, *up)
+
+        graph = capture(gate_up, 16)
+        graph.replay()
+        torch.cuda.synchronize()
+        per_launch = time_graph(graph, 10) / 160
+        algorithmic = 2 * hidden * inter * (0.5 + 4 / 64) + x1.numel() * 2 + inter * 2
+        achieved = algorithmic / per_launch / 1e9
+        roofline = {
+            "kernel": "gate|up SwiGLU projection, M=1 (" + B.mlx_affine_swiglu_dispatches()[0]["algorithm"] + ")",
+            "bound": "hbm",
+            "achieved": achieved,
+            "peak": hbm_peak,
+            "unit": "GB/s",
+            "frac": achieved / hbm_peak,
+            "peak_kind": f"of {peak_kind}",
+            "traffic": None,
+            "algorithmic_bytes_per_launch": int(algorithmic),
+            "us_per_launch": per_launch * 1e6,
+        }
+        del gate_sets
+
+    # ---- end to end through the public executor with host buffers ---------------------------------
+    def e2e_step():
+        for m in sweep:
+            hx, hr = host_inputs[m]
+            x = hx.to(device, non_blocking=True)
+            r = hr.to(device, non_blocking=True)
+            y = next_executor()(x, r)
+            host_outputs[m].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_seconds = (time.perf_counter() - start) / args.steps
+    if distributed:
+        t = torch.tensor([e2e_seconds], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_seconds = float(t.item())
+    h2d = sum(2 * m * hidden * 2 for m in sweep)
+    d2h = sum(m * hidden * 2 for m in sweep)
+
+    # ---- CPU baseline (rank 0, single-GPU run only) -----------------------------------------------
+    cpu_baseline = None
+    if rank == 0 and not tp:
+        times, cores = cpu_sweep_seconds(hidden, inter, sweep, 3)
+        cpu_seconds = min(times)
+        cpu_baseline = {"value": total_bytes / cpu_seconds / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                        "sample": f"3 full sweeps M={list(sweep)} of the same MLP (best), C + OpenMP port of the "
+                                  "reference semantics; MLX-CPU is unavailable on this box"}
+
+    if rank == 0:
+        kernels_per_mlp = 2
+        line = {
+            "metric": "int4_fused_mlp_weight_GBps",
+            "value": value,
+            "unit": "GB/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": step_seconds * 1e3,
+            "higher_is_better": True,
+            "scaling": "strong" if tp else "weak",
+            "vs_baseline": None,
+            "dtype": "bf16 activations, u4 weights, fp32 accumulate",
+            "data": "synthetic",
+            "config": workload_config(hidden, inter, sweep, world,
+                                      f"rotating {copies} weight sets ({copies * local_bytes / 1e6:.0f} MB per GPU) "
+                                      f"> 2x L2 ({l2_bytes / 1e6:.0f} MB)"),
+            "tokens_per_s": sum(sweep) / step_seconds,
+            "frac_of_hbm_peak": (local_bytes * len(sweep) / step_seconds / 1e9) / hbm_peak,
+            "sweep": detail,
+            "roofline": roofline,
+            "cpu_baseline": cpu_baseline,
+            "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_seconds * 1e3},
+            "gpu_launches": kernels_per_mlp * len(sweep) * args.steps,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line))
+    if distributed:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        if args.steps > 20:
+            args.steps = 20  # each CPU step is a full sweep (~1 s); keep the run within minutes
+        if args.warmup > 3:
+            args.warmup = 3
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -248,6 +248,7 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 bias_next = __ldg(bias_row + kb_begin + i + 1);
             }
             if (!ptx::mbar_wait(&ring_full[s], phase, abort_flag, kWaitRingFull)) break;
+            __syncwarp();
             const uint8_t* stage = ring + s * Cfg::kStageBytes;
             const uint4* wsrc = reinterpret_cast<const uint4*>(stage + t * Cfg::kWTileBytes + r * 32);
             const uint4 w_lo = wsrc[0], w_hi = wsrc[1];
@@ -260,12 +261,17 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 if (task < kMPad * 8)
                     xv[j] = *reinterpret_cast<const uint4*>(stage + Cfg::kWBytes + task * 16);
             }
+            // The slot is about to be overwritten by TMA (async proxy) while it was just read with
+            // ordinary loads (generic proxy): without this cross-proxy fence the refill was observed
+            // to overtake the reads when the ring is only two slots deep.
+            ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&ring_empty[s]);  // ring slot may be refilled
 
             const int a = i % Cfg::kAbStages;
             const uint32_t aphase = (i / Cfg::kAbStages) & 1;
             if (!ptx::mbar_wait(&ab_empty[a], aphase ^ 1, abort_flag, kWaitAbEmpty)) break;
+            __syncwarp();  // the .sync.aligned tcgen05 instructions below need a converged warp
             ptx::tc_fence_after_sync();
 
             const __nv_bfloat162 scale2 = bits_bf162(scale_bits | (scale_bits << 16));
@@ -312,7 +318,10 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
         }
 
         // -------------------------------------------------------------- accumulators -> smem
-        const bool ok = nkb > 0 && ptx::mbar_wait(acc_full, 0, abort_flag, kWaitAccFull);
+        // Lanes can leave a polling loop, or the lane-0 arrive above, at different times; the
+        // aligned TMEM loads need every lane of the warp together, with one verdict.
+        __syncwarp();
+        const bool ok = __all_sync(0xFFFFFFFFu, nkb > 0 && ptx::mbar_wait(acc_full, 0, abort_flag, kWaitAccFull));
         ptx::tc_fence_after_sync();
         float* staging = reinterpret_cast<float*>(smem);
 #pragma unroll
@@ -365,13 +374,17 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
             }
         }
     }
+    __syncwarp();
     if (ksplit > 1) {
         ptx::cluster_arrive();
         ptx::cluster_wait();
     } else {
         __syncthreads();
     }
-    if (warp == Cfg::kMmaWarp) ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if (warp == Cfg::kMmaWarp) {
+        __syncwarp();
+        ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
 }
 
 // ------------------------------------------------------------------------------- host side
