@@ -26,6 +26,8 @@ def mlx_rms_norm(values, weight, eps, *, autotune=True):
     x = values.contiguous()
     w = weight.contiguous()
     out = torch.empty_like(x)
+    if x.numel() == 0:
+        return out
     code = library().mt_rmsnorm(pointer(x), pointer(w), pointer(out), rows_of(x), x.shape[-1],
                                 ctypes.c_float(float(eps)), stream_pointer(x.device))
     _lib.check(code, "mlx_rms_norm")
@@ -47,6 +49,8 @@ def mlx_add_rms_norm(values, residual, weight, eps, *, autotune=True):
     w = weight.contiguous()
     summed = torch.empty_like(x)
     normalized = torch.empty_like(x)
+    if x.numel() == 0:
+        return summed, normalized
     code = library().mt_add_rmsnorm(pointer(x), pointer(r), pointer(w), pointer(summed),
                                     pointer(normalized), rows_of(x), x.shape[-1],
                                     ctypes.c_float(float(eps)), stream_pointer(x.device))

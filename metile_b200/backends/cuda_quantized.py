@@ -218,8 +218,9 @@ def mlx_affine_mlp_executor(sample_values, gate_weight, gate_scales, gate_biases
         raise ValueError("residual must match the MLP output shape and dtype")
     lib = library()
     device = sample_values.device
-    pointers = [pointer(t) for t in (gate_weight, gate_scales, gate_biases, up_weight, up_scales,
-                                     up_biases, down_weight, down_scales, down_biases)]
+    bound = (gate_weight, gate_scales, gate_biases, up_weight, up_scales, up_biases, down_weight,
+             down_scales, down_biases)
+    pointers = [pointer(t) for t in bound]
 
     def execute(values, residual=None):
         if values.dtype != torch.bfloat16 or values.shape[-1] != hidden_features:
@@ -239,6 +240,8 @@ def mlx_affine_mlp_executor(sample_values, gate_weight, gate_scales, gate_biases
         _lib.check(code, name)
         return out.reshape(values.shape)
 
+    # The raw pointers above stay valid only while the tensors live: the callable owns them.
+    execute.weights = bound
     return execute
 
 

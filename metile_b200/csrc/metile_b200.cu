@@ -215,12 +215,14 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
 
 int mt_add_rmsnorm(const void* x, const void* residual, const void* weight, void* sum_out, void* norm_out, int rows,
                    int H, float eps, void* stream) {
+    if (rows == 0) return MT_OK;
     if (!residual) return MT_ERR_NULL;
     if (!device_is_sm100()) return MT_ERR_DEVICE;
     return launch_add_rmsnorm(x, residual, weight, sum_out, norm_out, rows, H, eps, static_cast<cudaStream_t>(stream));
 }
 
 int mt_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, float eps, void* stream) {
+    if (rows == 0) return MT_OK;
     if (!device_is_sm100()) return MT_ERR_DEVICE;
     return launch_add_rmsnorm(x, nullptr, weight, nullptr, out, rows, H, eps, static_cast<cudaStream_t>(stream));
 }
