@@ -13,13 +13,17 @@
 // (128 TMEM lanes), the activation rows (padded to 16/32/64/128) are its N dimension, K advances
 // 16 elements per instruction, 64 (one quantisation group) per pipeline step.
 //
-//   producer lane  : TMA (cp.async.bulk.tensor, no multicast) packed weight tile(s) 128x32 B and
-//                    the activation tile kMPad x 128 B into a shared-memory ring
-//   dequant warps  : one thread per weight row; nibbles -> bf16x2 with the 0x4300 exponent trick
+//   producer lane  : TMA (cp.async.bulk.tensor, no multicast, 128B swizzle) packed weight tile(s) of
+//                    128 rows x 128 B = four k-blocks per ring slot; boxes with a 32-byte inner
+//                    extent were measured to be limited by the TMA request rate, not by HBM
+//   dequant warps  : 16 warps in groups of four (one group = the 128 rows of one tile); with kT
+//                    tiles per CTA there are kDepth = 4/kT groups per tile and group d handles the
+//                    k-blocks i = d, d+kDepth, ... so several k-blocks are in flight per SM.
+//                    One thread per weight row; nibbles -> bf16x2 with the 0x4300 exponent trick
 //                    ((w>>4i)&0x000F000F | 0x43004300 = 128+q), q = v-128, w = fma(q, scale, bias)
 //                    (one rounding: RN_bf16(scale*q+bias)); result either stored to TMEM as the A
-//                    operand (kTmemA) or to 128B-swizzled shared memory; also copies the activation
-//                    tile into the swizzled B tile with the same within-8 element order the unpack
+//                    operand (kTmemA) or to 128B-swizzled shared memory; also loads the activation
+//                    rows (L2-resident) and writes the swizzled B tile with the same within-8 element order the unpack
 //                    produces (e0,e4,e1,e5,e2,e6,e3,e7) -- a K permutation applied to both operands
 //                    leaves the contraction unchanged
 //   MMA lane       : tcgen05.mma kind::f16 (bf16 x bf16 -> fp32 in TMEM), tcgen05.commit
@@ -40,7 +44,8 @@
 namespace mt {
 
 constexpr int kUmmaTileRows = 128;
-constexpr int kUmmaBlockK = 64;
+constexpr int kUmmaBlockK = 64;      // one quantisation group per MMA pipeline step
+constexpr int kUmmaKBlocksPerSlot = 4;  // a ring slot holds 4 k-blocks: 128 B of packed nibbles per row
 
 constexpr int pow2_at_least(int v) {
     int p = 32;
@@ -50,47 +55,53 @@ constexpr int pow2_at_least(int v) {
 
 template <int kT, int kMPad, bool kTmemA>
 struct UmmaConfig {
-    static constexpr int kDequantWarps = 4 * kT;
+    static constexpr int kDepth = 4 / kT;                           // dequant groups per tile
+    static constexpr int kDequantWarps = 16;                        // 4 warps x kT tiles x kDepth
+    static constexpr int kWarpsPerKBlock = 4 * kT;                  // warps that serve one k-block
     static constexpr int kProducerWarp = kDequantWarps;
     static constexpr int kMmaWarp = kDequantWarps + 1;
     static constexpr int kThreads = (kDequantWarps + 2) * 32;
-    static constexpr int kWTileBytes = kUmmaTileRows * 32;          // one packed tile, one k-block
-    static constexpr int kWBytes = kT * kWTileBytes;
-    static constexpr int kXBytes = kMPad * 128;
-    static constexpr int kStageBytes = kWBytes + kXBytes;
-    static constexpr int kATileBytes = kUmmaTileRows * 128;         // one dequantised bf16 tile
+    static constexpr int kWTileBytes = kUmmaTileRows * 128;         // one packed tile, four k-blocks
+    static constexpr int kSlotBytes = kT * kWTileBytes;
+    static constexpr int kATileBytes = kUmmaTileRows * 128;         // one dequantised bf16 tile, one k-block
     static constexpr int kABytes = kTmemA ? 0 : kT * kATileBytes;
     static constexpr int kBBytes = kMPad * 128;
     static constexpr int kAbBytes = kABytes + kBBytes;
-    static constexpr int kAbStages = kTmemA ? 3 : 2;
+    static constexpr int kAbStages = kTmemA ? 4 : kDepth;
     static constexpr int kAccCols = kT * kMPad;
     static constexpr int kATmemCols = kTmemA ? kAbStages * kT * 32 : 0;
     static constexpr int kTmemCols = pow2_at_least(kAccCols + kATmemCols);
-    // Shared-memory target: two CTAs per SM while their TMEM fits twice, else one.
-    static constexpr int kRingTarget = (kTmemCols <= 256 ? 106 : 196) * 1024 - kAbStages * kAbBytes;
-    static constexpr int kStagesRaw = kRingTarget / kStageBytes;
+    // One CTA per SM (18 warps).  The ring takes what shared memory is left, up to 8 slots.
+    static constexpr int kRingTarget = 196 * 1024 - kAbStages * kAbBytes;
+    static constexpr int kStagesRaw = kRingTarget / kSlotBytes;
     static constexpr int kStages = kStagesRaw < 2 ? 2 : (kStagesRaw > 8 ? 8 : kStagesRaw);
-    static constexpr int kRingBytes = kStages * kStageBytes;
+    static constexpr int kRingBytes = kStages * kSlotBytes;
     static constexpr int kStagingBytes = kT * kMPad * kUmmaTileRows * 4;
     static constexpr int kDataBytesRaw = kRingBytes + kAbStages * kAbBytes;
-    static constexpr int kDataBytes = kDataBytesRaw > kStagingBytes ? kDataBytesRaw : kStagingBytes;
+    static constexpr int kDataBytesMin = kDataBytesRaw > kStagingBytes ? kDataBytesRaw : kStagingBytes;
+    // TMEM columns x resident CTAs must never exceed 512: a later CTA's tcgen05.alloc would wait
+    // for an earlier CTA to finish.  Every CTA therefore asks for more than half of an SM's
+    // shared memory, which keeps it alone on its SM.
+    static constexpr int kFloorBytes = (227 * 1024) / 2 + 2048;
+    static constexpr int kDataBytes = kDataBytesMin < kFloorBytes ? kFloorBytes : kDataBytesMin;
     static constexpr int kBarrierBytes = 8 * (2 * kStages + 2 * kAbStages + 1) + 16;
     static constexpr int kSmemBytes = 1024 + kDataBytes + kBarrierBytes;
-    // TMEM columns x resident CTAs must stay within 512, or tcgen05.alloc of a later CTA would
-    // wait for an earlier one to finish.  Shared memory bounds the residency.
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-    static_assert(kStageBytes % 1024 == 0 && kWBytes % 1024 == 0 && kAbBytes % 1024 == 0, "1024 B alignment");
-    static_assert((227 * 1024 / kSmemBytes) * kTmemCols <= 512, "TMEM over-subscription");
+    static_assert(kSlotBytes % 1024 == 0 && kAbBytes % 1024 == 0, "1024 B alignment");
+    static_assert(2 * kSmemBytes > 227 * 1024, "a second CTA must not fit beside this one");
+    static_assert(kAbStages % kDepth == 0, "each depth group owns whole operand stages");
+    static_assert(kUmmaKBlocksPerSlot % kDepth == 0, "a group sees the same k-blocks in every slot");
 };
 
 struct UmmaParams {
-    CUtensorMap w_map[2];  // packed weights, uint32 [N, K/8], box {8, 128}
-    CUtensorMap x_map;     // activations, bf16 [M, K], box {64, kMPad}
+    CUtensorMap w_map[2];  // packed weights, uint32 [N, K/8], box {32, 128}, 128B swizzle
+    const uint16_t* x;     // activations, bf16 [M, K]
     const uint16_t* scales[2];
     const uint16_t* biases[2];
     const uint16_t* residual;
     uint16_t* out;
     int M, K, N, ksplit;
+    long long* timeline;  // diagnostic: block 0 records clock64() per phase when non-null
 };
 
 enum : unsigned int {
@@ -117,6 +128,20 @@ __device__ __forceinline__ void dequant_word_bf16(uint32_t w, __nv_bfloat162 sca
     }
 }
 
+__device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// Diagnostic phase stamps (cycle counter of block 0's SM); a null pointer disables them.
+#define MT_STAMP(slot)                                                      \
+    do {                                                                    \
+        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[slot] = clock64(); \
+    } while (0)
+
 template <int kT, int kMPad, bool kTmemA, bool kSwiglu>
 __global__ void __launch_bounds__(UmmaConfig<kT, kMPad, kTmemA>::kThreads, 1)
 affine_umma_kernel(const __grid_constant__ UmmaParams p) {
@@ -142,17 +167,23 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     const int tile = blockIdx.x / ksplit;
     const int n0 = tile * kUmmaTileRows;
     const int kblocks = p.K / kUmmaBlockK;
-    const int kb_begin = (int)(((long long)kblocks * rank) / ksplit);
-    const int kb_end = (int)(((long long)kblocks * (rank + 1)) / ksplit);
+    // The K range is cut between the CTAs of a cluster in whole ring slots (4 k-blocks).
+    const int slots_total = (kblocks + kUmmaKBlocksPerSlot - 1) / kUmmaKBlocksPerSlot;
+    const int slot_begin = (int)(((long long)slots_total * rank) / ksplit);
+    const int slot_end = (int)(((long long)slots_total * (rank + 1)) / ksplit);
+    const int nslots = slot_end - slot_begin;
+    const int kb_begin = slot_begin * kUmmaKBlocksPerSlot;
+    const int kb_end = min(slot_end * kUmmaKBlocksPerSlot, kblocks);
     const int nkb = kb_end - kb_begin;
 
     if (threadIdx.x == 0) {
+        MT_STAMP(0);
         for (int i = 0; i < Cfg::kStages; ++i) {
             ptx::mbar_init(&ring_full[i], 1);
             ptx::mbar_init(&ring_empty[i], Cfg::kDequantWarps);
         }
         for (int i = 0; i < Cfg::kAbStages; ++i) {
-            ptx::mbar_init(&ab_full[i], Cfg::kDequantWarps);
+            ptx::mbar_init(&ab_full[i], Cfg::kWarpsPerKBlock);
             ptx::mbar_init(&ab_empty[i], 1);
         }
         ptx::mbar_init(acc_full, 1);
@@ -167,32 +198,33 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) MT_STAMP(1);
 
     if (warp == Cfg::kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             ptx::prefetch_tensor_map(&p.w_map[0]);
             if (kT == 2) ptx::prefetch_tensor_map(&p.w_map[1]);
-            ptx::prefetch_tensor_map(&p.x_map);
             int issued = 0;
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % Cfg::kStages;
-                const uint32_t phase = (i / Cfg::kStages) & 1;
+            for (int st = 0; st < nslots; ++st) {
+                const int s = st % Cfg::kStages;
+                const uint32_t phase = (st / Cfg::kStages) & 1;
                 if (!ptx::mbar_wait(&ring_empty[s], phase ^ 1, abort_flag, kWaitRingEmpty)) break;
-                ptx::mbar_expect_tx(&ring_full[s], Cfg::kStageBytes);
-                uint8_t* stage = ring + s * Cfg::kStageBytes;
-                const int kb = kb_begin + i;
+                ptx::mbar_expect_tx(&ring_full[s], Cfg::kSlotBytes);
+                uint8_t* slot = ring + s * Cfg::kSlotBytes;
 #pragma unroll
                 for (int t = 0; t < kT; ++t)
-                    ptx::tma_load_2d(stage + t * Cfg::kWTileBytes, &p.w_map[t], kb * 8, n0, &ring_full[s]);
-                ptx::tma_load_2d(stage + Cfg::kWBytes, &p.x_map, kb * kUmmaBlockK, 0, &ring_full[s]);
+                    ptx::tma_load_2d(slot + t * Cfg::kWTileBytes, &p.w_map[t], (slot_begin + st) * 32, n0,
+                                     &ring_full[s]);
                 ++issued;
+                if (st == 0) MT_STAMP(2);
             }
+            MT_STAMP(3);
             if (*abort_flag) {
                 // Let copies already in flight land before the CTA may exit.
                 const int first = issued > Cfg::kStages ? issued - Cfg::kStages : 0;
-                for (int i = first; i < issued; ++i)
-                    ptx::mbar_wait(&ring_full[i % Cfg::kStages], (i / Cfg::kStages) & 1, abort_flag, kWaitDrain);
+                for (int st = first; st < issued; ++st)
+                    ptx::mbar_wait(&ring_full[st % Cfg::kStages], (st / Cfg::kStages) & 1, abort_flag, kWaitDrain);
             }
         }
     } else if (warp == Cfg::kMmaWarp) {
@@ -203,6 +235,7 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 const int a = i % Cfg::kAbStages;
                 const uint32_t phase = (i / Cfg::kAbStages) & 1;
                 if (!ptx::mbar_wait(&ab_full[a], phase, abort_flag, kWaitAbFull)) break;
+                if (i == 0) MT_STAMP(7);
                 ptx::tc_fence_after_sync();
                 const uint32_t b_addr = ptx::smem_u32(ab + a * Cfg::kAbBytes + Cfg::kABytes);
 #pragma unroll
@@ -225,117 +258,169 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 ptx::umma_commit(&ab_empty[a]);
             }
             ptx::umma_commit(acc_full);
+            MT_STAMP(8);
         }
     } else {
         // ------------------------------------------------------------------ dequant warps
-        const int t = warp >> 2;                       // which tile (gate / up) this warp feeds
+        const int group = warp >> 2;                   // four warps = one group = 128 rows
+        const int t = kT == 2 ? (group & 1) : 0;       // which tile (gate / up) this group feeds
+        const int depth = kT == 2 ? (group >> 1) : group;  // which k-blocks: i = depth, depth+kDepth, ...
         const int r = ((warp & 3) << 5) | lane;        // weight row inside the tile == TMEM lane
         const int n = min(n0 + r, p.N - 1);            // rows past N were zero-filled by TMA
-        const uint16_t* scale_row = p.scales[t] + (size_t)n * kblocks;
-        const uint16_t* bias_row = p.biases[t] + (size_t)n * kblocks;
-        const int tid = threadIdx.x;                   // 0 .. 128*kT-1
+        const uint16_t* scale_row = p.scales[t] + (size_t)n * kblocks + kb_begin;
+        const uint16_t* bias_row = p.biases[t] + (size_t)n * kblocks + kb_begin;
+        const int tid = t * 128 + r;                   // index among the threads serving one k-block
+        constexpr int kKBlockThreads = Cfg::kWarpsPerKBlock * 32;
+        constexpr int kXTasks = (kMPad * 8 + kKBlockThreads - 1) / kKBlockThreads;
+        const int x_tasks = p.M * 8;                   // 16-byte chunks (8 k) of the real rows only
+        const uint16_t* x_base = p.x + (size_t)kb_begin * kUmmaBlockK;
         uint32_t scale_next = 0, bias_next = 0;
-        if (nkb > 0) {
-            scale_next = __ldg(scale_row + kb_begin);
-            bias_next = __ldg(bias_row + kb_begin);
+        // Activation chunks come straight from global memory (L2-resident) and are fetched one
+        // k-block of this group ahead, so their latency never sits on the dequant path.
+        uint4 xv_next[kXTasks];
+        auto load_x = [&](int kblock) {
+#pragma unroll
+            for (int q = 0; q < kXTasks; ++q) {
+                const int task = tid + q * kKBlockThreads;
+                if (task < x_tasks)
+                    xv_next[q] = ldg_nc_u4(x_base + (size_t)(task >> 3) * p.K + (size_t)kblock * kUmmaBlockK +
+                                           (task & 7) * 8);
+            }
+        };
+        if (depth < nkb) {
+            scale_next = __ldg(scale_row + depth);
+            bias_next = __ldg(bias_row + depth);
+            load_x(depth);
         }
-        for (int i = 0; i < nkb; ++i) {
-            const int s = i % Cfg::kStages;
-            const uint32_t phase = (i / Cfg::kStages) & 1;
-            const uint32_t scale_bits = scale_next, bias_bits = bias_next;
-            if (i + 1 < nkb) {
-                scale_next = __ldg(scale_row + kb_begin + i + 1);
-                bias_next = __ldg(bias_row + kb_begin + i + 1);
-            }
-            if (!ptx::mbar_wait(&ring_full[s], phase, abort_flag, kWaitRingFull)) break;
-            __syncwarp();
-            const uint8_t* stage = ring + s * Cfg::kStageBytes;
-            const uint4* wsrc = reinterpret_cast<const uint4*>(stage + t * Cfg::kWTileBytes + r * 32);
-            const uint4 w_lo = wsrc[0], w_hi = wsrc[1];
-            // Activation tile: each thread moves kXTasks 16-byte chunks (8 consecutive k of one row).
-            constexpr int kXTasks = (kMPad * 8 + Cfg::kDequantWarps * 32 - 1) / (Cfg::kDequantWarps * 32);
-            uint4 xv[kXTasks];
+        bool alive = true;
+        for (int st = 0; st < nslots && alive; ++st) {
+            const int s = st % Cfg::kStages;
+            const uint32_t phase = (st / Cfg::kStages) & 1;
+            const uint8_t* slot = ring + s * Cfg::kSlotBytes;
+            bool waited = false;
 #pragma unroll
-            for (int j = 0; j < kXTasks; ++j) {
-                const int task = tid + j * Cfg::kDequantWarps * 32;
-                if (task < kMPad * 8)
-                    xv[j] = *reinterpret_cast<const uint4*>(stage + Cfg::kWBytes + task * 16);
-            }
-            // The slot is about to be overwritten by TMA (async proxy) while it was just read with
-            // ordinary loads (generic proxy): without this cross-proxy fence the refill was observed
-            // to overtake the reads when the ring is only two slots deep.
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&ring_empty[s]);  // ring slot may be refilled
-
-            const int a = i % Cfg::kAbStages;
-            const uint32_t aphase = (i / Cfg::kAbStages) & 1;
-            if (!ptx::mbar_wait(&ab_empty[a], aphase ^ 1, abort_flag, kWaitAbEmpty)) break;
-            __syncwarp();  // the .sync.aligned tcgen05 instructions below need a converged warp
-            ptx::tc_fence_after_sync();
-
-            const __nv_bfloat162 scale2 = bits_bf162(scale_bits | (scale_bits << 16));
-            const __nv_bfloat162 bias2 = bits_bf162(bias_bits | (bias_bits << 16));
-            uint32_t wq[32];
-            const uint32_t words[8] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w, w_hi.x, w_hi.y, w_hi.z, w_hi.w};
-#pragma unroll
-            for (int c = 0; c < 8; ++c) dequant_word_bf16(words[c], scale2, bias2, &wq[4 * c]);
-
-            uint8_t* ab_stage = ab + a * Cfg::kAbBytes;
-            if constexpr (kTmemA) {
-                const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + Cfg::kAccCols +
-                                        (a * kT + t) * 32;
-                ptx::tmem_st16(a_tmem, &wq[0]);
-                ptx::tmem_st16(a_tmem + 16, &wq[16]);
-            } else {
-                uint8_t* a_row = ab_stage + t * Cfg::kATileBytes + r * 128;
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *reinterpret_cast<uint4*>(a_row + ((c ^ (r & 7)) << 4)) =
-                        make_uint4(wq[4 * c], wq[4 * c + 1], wq[4 * c + 2], wq[4 * c + 3]);
-            }
-            uint8_t* b_tile = ab_stage + Cfg::kABytes;
-#pragma unroll
-            for (int j = 0; j < kXTasks; ++j) {
-                const int task = tid + j * Cfg::kDequantWarps * 32;
-                if (task < kMPad * 8) {
-                    const int row = task >> 3, c = task & 7;
-                    uint4 o;
-                    o.x = __byte_perm(xv[j].x, xv[j].z, 0x5410);  // (x0, x4)
-                    o.y = __byte_perm(xv[j].x, xv[j].z, 0x7632);  // (x1, x5)
-                    o.z = __byte_perm(xv[j].y, xv[j].w, 0x5410);  // (x2, x6)
-                    o.w = __byte_perm(xv[j].y, xv[j].w, 0x7632);  // (x3, x7)
-                    *reinterpret_cast<uint4*>(b_tile + row * 128 + ((c ^ (row & 7)) << 4)) = o;
+            for (int jj = 0; jj < kUmmaKBlocksPerSlot / Cfg::kDepth; ++jj) {
+                const int j = depth + jj * Cfg::kDepth;              // k-block inside the slot
+                const int i = st * kUmmaKBlocksPerSlot + j;          // k-block inside this CTA's range
+                if (i >= nkb) break;
+                const bool probe = (p.timeline != nullptr && blockIdx.x == 0 && i == 8 && threadIdx.x == 32);
+                if (probe) MT_STAMP(16);
+                const int a = i % Cfg::kAbStages;
+                const uint32_t aphase = (i / Cfg::kAbStages) & 1;
+                const uint32_t scale_bits = scale_next, bias_bits = bias_next;
+                if (i + Cfg::kDepth < nkb) {
+                    scale_next = __ldg(scale_row + i + Cfg::kDepth);
+                    bias_next = __ldg(bias_row + i + Cfg::kDepth);
                 }
+                uint4 xv[kXTasks];
+#pragma unroll
+                for (int q = 0; q < kXTasks; ++q) xv[q] = xv_next[q];
+                if (i + Cfg::kDepth < nkb) load_x(i + Cfg::kDepth);
+                if (!waited) {
+                    if (!ptx::mbar_wait(&ring_full[s], phase, abort_flag, kWaitRingFull)) { alive = false; break; }
+                    waited = true;
+                    if (st == 0 && threadIdx.x == 0) MT_STAMP(4);
+                }
+                if (probe) MT_STAMP(17);
+                if (!ptx::mbar_wait(&ab_empty[a], aphase ^ 1, abort_flag, kWaitAbEmpty)) { alive = false; break; }
+                __syncwarp();  // the .sync.aligned tcgen05 instructions below need a converged warp
+                ptx::tc_fence_after_sync();
+                if (probe) MT_STAMP(18);
+
+                // 32 B of this row for k-block j: 16-byte chunks 2j and 2j+1, XOR-swizzled by the row.
+                const uint8_t* wrow = slot + t * Cfg::kWTileBytes + r * 128;
+                const uint4 w_lo = *reinterpret_cast<const uint4*>(wrow + (((2 * j) ^ (r & 7)) << 4));
+                const uint4 w_hi = *reinterpret_cast<const uint4*>(wrow + (((2 * j + 1) ^ (r & 7)) << 4));
+                const __nv_bfloat162 scale2 = bits_bf162(scale_bits | (scale_bits << 16));
+                const __nv_bfloat162 bias2 = bits_bf162(bias_bits | (bias_bits << 16));
+                uint32_t wq[32];
+                const uint32_t words[8] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w, w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+#pragma unroll
+                for (int c = 0; c < 8; ++c) dequant_word_bf16(words[c], scale2, bias2, &wq[4 * c]);
+
+                uint8_t* ab_stage = ab + a * Cfg::kAbBytes;
+                if (probe) p.timeline[19] = clock64() + (wq[31] & 1);
+                if constexpr (kTmemA) {
+                    const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + Cfg::kAccCols +
+                                            (a * kT + t) * 32;
+                    ptx::tmem_st16(a_tmem, &wq[0]);
+                    ptx::tmem_st16(a_tmem + 16, &wq[16]);
+                } else {
+                    uint8_t* a_row = ab_stage + t * Cfg::kATileBytes + r * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4*>(a_row + ((c ^ (r & 7)) << 4)) =
+                            make_uint4(wq[4 * c], wq[4 * c + 1], wq[4 * c + 2], wq[4 * c + 3]);
+                }
+                // Activation chunks -> swizzled B tile with the element order the unpack produces.
+                // Rows past M are never written: an output column depends on its own B row only.
+                uint8_t* b_tile = ab_stage + Cfg::kABytes;
+#pragma unroll
+                for (int q = 0; q < kXTasks; ++q) {
+                    const int task = tid + q * kKBlockThreads;
+                    if (task < x_tasks) {
+                        const int row = task >> 3, c = task & 7;
+                        uint4 o;
+                        o.x = __byte_perm(xv[q].x, xv[q].z, 0x5410);  // (x0, x4)
+                        o.y = __byte_perm(xv[q].x, xv[q].z, 0x7632);  // (x1, x5)
+                        o.z = __byte_perm(xv[q].y, xv[q].w, 0x5410);  // (x2, x6)
+                        o.w = __byte_perm(xv[q].y, xv[q].w, 0x7632);  // (x3, x7)
+                        *reinterpret_cast<uint4*>(b_tile + row * 128 + ((c ^ (row & 7)) << 4)) = o;
+                    }
+                }
+                if (probe) MT_STAMP(20);
+                // One cross-proxy fence covers both directions: the tiles written above become visible
+                // to the MMA (async proxy), and the ring slot read above with ordinary loads may later be
+                // overwritten by TMA (async proxy).  Releasing a slot without such a fence was observed
+                // to let the refill overtake the reads.
+                ptx::fence_proxy_async_smem();
+                if (probe) MT_STAMP(21);
+                if constexpr (kTmemA) {
+                    ptx::tc_wait_st();
+                    ptx::tc_fence_before_sync();
+                }
+                if (probe) MT_STAMP(22);
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&ab_full[a]);
+                if (probe) MT_STAMP(23);
+                if (i == 0 && threadIdx.x == 0) MT_STAMP(5);
             }
-            ptx::fence_proxy_async_smem();
-            if constexpr (kTmemA) {
-                ptx::tc_wait_st();
-                ptx::tc_fence_before_sync();
+            if (!alive) break;
+            if (!waited) {
+                // No k-block of this slot belongs to this group (ragged tail): still observe the
+                // refill before releasing, so the arrival is counted in the right phase.
+                if (!ptx::mbar_wait(&ring_full[s], phase, abort_flag, kWaitRingFull)) break;
             }
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&ab_full[a]);
+            if (lane == 0) ptx::mbar_arrive(&ring_empty[s]);
         }
 
+        if (threadIdx.x == 0) MT_STAMP(6);
         // -------------------------------------------------------------- accumulators -> smem
-        // Lanes can leave a polling loop, or the lane-0 arrive above, at different times; the
+        // Lanes can leave a polling loop, or a lane-0 arrive above, at different times; the
         // aligned TMEM loads need every lane of the warp together, with one verdict.
         __syncwarp();
-        const bool ok = __all_sync(0xFFFFFFFFu, nkb > 0 && ptx::mbar_wait(acc_full, 0, abort_flag, kWaitAccFull));
-        ptx::tc_fence_after_sync();
-        float* staging = reinterpret_cast<float*>(smem);
+        if (depth == 0) {
+            const bool ok =
+                __all_sync(0xFFFFFFFFu, nkb > 0 && ptx::mbar_wait(acc_full, 0, abort_flag, kWaitAccFull));
+            ptx::tc_fence_after_sync();
+            if (threadIdx.x == 0) MT_STAMP(9);
+            float* staging = reinterpret_cast<float*>(smem);
 #pragma unroll
-        for (int c0 = 0; c0 < kMPad; c0 += 16) {
-            uint32_t v[16];
-            if (ok) {
-                ptx::tmem_ld16(tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + t * kMPad + c0, v);
-                ptx::tc_wait_ld();
-            } else {
+            for (int c0 = 0; c0 < kMPad; c0 += 16) {
+                uint32_t v[16];
+                if (ok) {
+                    ptx::tmem_ld16(tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + t * kMPad + c0, v);
+                    ptx::tc_wait_ld();
+                } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = 0u;
+                    for (int j = 0; j < 16; ++j) v[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c0 + j < p.M) staging[(t * kMPad + c0 + j) * kUmmaTileRows + r] = __uint_as_float(v[j]);
             }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) staging[(t * kMPad + c0 + j) * kUmmaTileRows + r] = __uint_as_float(v[j]);
+            if (threadIdx.x == 0) MT_STAMP(10);
         }
     }
 
@@ -348,12 +433,13 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     } else {
         __syncthreads();
     }
+    if (threadIdx.x == 0) MT_STAMP(11);
     if (warp < Cfg::kDequantWarps) {
         const int r = threadIdx.x & 127;
-        const int group = threadIdx.x >> 7;        // kT groups of 128 threads
+        const int part = threadIdx.x >> 7;         // four groups of 128 threads share the rows
         const int n = n0 + r;
         const uint32_t staging_addr = ptx::smem_u32(smem);
-        for (int m = rank + ksplit * group; m < p.M; m += ksplit * kT) {
+        for (int m = rank + ksplit * part; m < p.M; m += ksplit * 4) {
             float first = 0.0f, second = 0.0f;
             if (ksplit > 1) {
                 for (int j = 0; j < ksplit; ++j) {
@@ -374,6 +460,7 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
             }
         }
     }
+    if (threadIdx.x == 0) MT_STAMP(12);
     __syncwarp();
     if (ksplit > 1) {
         ptx::cluster_arrive();
@@ -381,6 +468,7 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     } else {
         __syncthreads();
     }
+    if (threadIdx.x == 0) MT_STAMP(13);
     if (warp == Cfg::kMmaWarp) {
         __syncwarp();
         ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
@@ -404,32 +492,78 @@ inline EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-inline bool encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t inner,
-                      uint64_t outer, uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer) {
+// Packed weights as a 2-D uint32 tensor [N, K/8]; box = 32 words (128 B, four k-blocks) x 128 rows,
+// 128-byte swizzle so that a thread reading "its" row's 32 bytes hits distinct banks.
+inline bool encode_weight_map(CUtensorMap* map, const void* base, int K, int N) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {row_bytes};
-    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint64_t dims[2] = {(cuuint64_t)K / 8, (cuuint64_t)N};
+    cuuint64_t strides[1] = {(cuuint64_t)K / 2};
+    cuuint32_t box[2] = {32, (cuuint32_t)kUmmaTileRows};
     cuuint32_t elem_strides[2] = {1, 1};
-    (void)elem_bytes;
-    return fn(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Cluster size along K: fill the SMs when there are few 128-row tiles.  Function of the tile
-// count and K only.
-inline int umma_ksplit(int tiles, int kblocks, int sm_count) {
+template <int kT, int kMPad, bool kTmemA, bool kSwiglu>
+inline cudaError_t configure_umma_instance() {
+    using Cfg = UmmaConfig<kT, kMPad, kTmemA>;
+    static bool configured[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 64 && configured[device]) return cudaSuccess;
+    const cudaError_t rc = cudaFuncSetAttribute(affine_umma_kernel<kT, kMPad, kTmemA, kSwiglu>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (rc == cudaSuccess && device < 64) configured[device] = true;
+    return rc;
+}
+
+// How many clusters of `size` CTAs of the 128-row instance can be resident at once.  Measured on
+// the largest instance of the family so that the answer, and with it the K split, does not depend
+// on the number of activation rows.
+template <int kT, bool kTmemA, bool kSwiglu>
+inline int umma_active_clusters(int size) {
+    static int cached[64][9] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 64 && cached[device][size]) return cached[device][size];
+    using Cfg = UmmaConfig<kT, 128, kTmemA>;
+    if (configure_umma_instance<kT, 128, kTmemA, kSwiglu>() != cudaSuccess) return 0;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(size * 64, 1, 1);
+    config.blockDim = dim3(Cfg::kThreads, 1, 1);
+    config.dynamicSmemBytes = Cfg::kSmemBytes;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = size;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    config.attrs = attrs;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, affine_umma_kernel<kT, 128, kTmemA, kSwiglu>, &config) !=
+        cudaSuccess)
+        clusters = 0;
+    if (device < 64) cached[device][size] = clusters > 0 ? clusters : -1;
+    return clusters;
+}
+
+// Cluster size along K.  A function of (tile count, K, kernel family, device) only -- never of the
+// number of activation rows.  cost = waves x (ring slots per CTA + a fixed prologue/epilogue term).
+template <int kT, bool kTmemA, bool kSwiglu>
+inline int umma_ksplit(int tiles, int slots_total) {
     int best = 1;
-    double best_score = -1.0;
-    for (int s = 1; s <= 8; s *= 2) {
-        if (s > 1 && kblocks / s < 4) break;
-        const long ctas = (long)tiles * s;
-        const long waves = (ctas + sm_count - 1) / sm_count;
-        const double score = (double)ctas / (double)(waves * sm_count) - 0.01 * (s - 1);
-        if (score > best_score + 1e-9) {
-            best_score = score;
+    long best_cost = -1;
+    for (int s = 1; s <= 8; ++s) {
+        if (s > slots_total) break;
+        const int active = umma_active_clusters<kT, kTmemA, kSwiglu>(s);
+        if (active <= 0) continue;
+        const long waves = (tiles + active - 1) / active;
+        const long per_cta = (slots_total + s - 1) / s;
+        const long cost = waves * (per_cta * 4 + 6);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
             best = s;
         }
     }
@@ -439,15 +573,7 @@ inline int umma_ksplit(int tiles, int kblocks, int sm_count) {
 template <int kT, int kMPad, bool kTmemA, bool kSwiglu>
 inline int launch_umma_instance(const UmmaParams& params, int tiles, cudaStream_t stream) {
     using Cfg = UmmaConfig<kT, kMPad, kTmemA>;
-    auto kernel = affine_umma_kernel<kT, kMPad, kTmemA, kSwiglu>;
-    static bool configured[64] = {};
-    int device = 0;
-    cudaGetDevice(&device);
-    if (device < 64 && !configured[device]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
-            return MT_ERR_LAUNCH;
-        configured[device] = true;
-    }
+    if (configure_umma_instance<kT, kMPad, kTmemA, kSwiglu>() != cudaSuccess) return MT_ERR_LAUNCH;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(tiles * params.ksplit, 1, 1);
     config.blockDim = dim3(Cfg::kThreads, 1, 1);
@@ -460,11 +586,15 @@ inline int launch_umma_instance(const UmmaParams& params, int tiles, cudaStream_
     attrs[0].val.clusterDim.z = 1;
     config.attrs = attrs;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, kernel, params) == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
+    return cudaLaunchKernelEx(&config, affine_umma_kernel<kT, kMPad, kTmemA, kSwiglu>, params) == cudaSuccess
+               ? MT_OK
+               : MT_ERR_LAUNCH;
 }
 
 template <int kT, bool kTmemA, bool kSwiglu>
-inline int launch_umma_mpad(const UmmaParams& params, int tiles, int mpad, cudaStream_t stream) {
+inline int launch_umma_family(UmmaParams& params, int tiles, int mpad, cudaStream_t stream) {
+    const int kblocks = params.K / kUmmaBlockK;
+    params.ksplit = umma_ksplit<kT, kTmemA, kSwiglu>(tiles, (kblocks + kUmmaKBlocksPerSlot - 1) / kUmmaKBlocksPerSlot);
     switch (mpad) {
         case 16: return launch_umma_instance<kT, 16, kTmemA, kSwiglu>(params, tiles, stream);
         case 32: return launch_umma_instance<kT, 32, kTmemA, kSwiglu>(params, tiles, stream);
@@ -474,6 +604,9 @@ inline int launch_umma_mpad(const UmmaParams& params, int tiles, int mpad, cudaS
     }
 }
 
+// Diagnostic: device buffer of at least 16 int64 that block 0 of every tcgen05 launch stamps.
+inline long long* g_timeline_buffer = nullptr;
+
 struct AffineWeights {
     const uint32_t* w;
     const uint16_t* scales;
@@ -482,13 +615,14 @@ struct AffineWeights {
 
 // x [M,K] bf16 (M <= 128), one weight triple (plain / residual) or two (gate, up -> SwiGLU).
 inline int launch_umma(const void* x, const AffineWeights* first, const AffineWeights* second, const void* residual,
-                       void* out, int M, int K, int N, bool tmem_a, int sm_count, cudaStream_t stream) {
+                       void* out, int M, int K, int N, bool tmem_a, cudaStream_t stream) {
     if (M < 1 || M > 128 || K % kUmmaBlockK || K < kUmmaBlockK || N < 1) return MT_ERR_SHAPE;
     if (!aligned_to(x, 16) || !aligned_to(first->w, 16) || (second && !aligned_to(second->w, 16))) return MT_ERR_ALIGN;
     const bool swiglu = second != nullptr;
     const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     const int tiles = (N + kUmmaTileRows - 1) / kUmmaTileRows;
     UmmaParams params;
+    params.x = static_cast<const uint16_t*>(x);
     params.scales[0] = first->scales;
     params.biases[0] = first->biases;
     params.scales[1] = swiglu ? second->scales : first->scales;
@@ -498,23 +632,16 @@ inline int launch_umma(const void* x, const AffineWeights* first, const AffineWe
     params.M = M;
     params.K = K;
     params.N = N;
-    params.ksplit = umma_ksplit(tiles, K / kUmmaBlockK, sm_count);
-    const uint64_t row_bytes = (uint64_t)K / 2;
-    if (!encode_2d(&params.w_map[0], CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, first->w, (uint64_t)K / 8, (uint64_t)N,
-                   row_bytes, 8, kUmmaTileRows))
-        return MT_ERR_LAUNCH;
-    if (!encode_2d(&params.w_map[1], CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, swiglu ? second->w : first->w,
-                   (uint64_t)K / 8, (uint64_t)N, row_bytes, 8, kUmmaTileRows))
-        return MT_ERR_LAUNCH;
-    if (!encode_2d(&params.x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2,
-                   kUmmaBlockK, (uint32_t)mpad))
-        return MT_ERR_LAUNCH;
+    params.ksplit = 1;
+    params.timeline = g_timeline_buffer;
+    if (!encode_weight_map(&params.w_map[0], first->w, K, N)) return MT_ERR_LAUNCH;
+    if (!encode_weight_map(&params.w_map[1], swiglu ? second->w : first->w, K, N)) return MT_ERR_LAUNCH;
     if (swiglu) {
-        return tmem_a ? launch_umma_mpad<2, true, true>(params, tiles, mpad, stream)
-                      : launch_umma_mpad<2, false, true>(params, tiles, mpad, stream);
+        return tmem_a ? launch_umma_family<2, true, true>(params, tiles, mpad, stream)
+                      : launch_umma_family<2, false, true>(params, tiles, mpad, stream);
     }
-    return tmem_a ? launch_umma_mpad<1, true, false>(params, tiles, mpad, stream)
-                  : launch_umma_mpad<1, false, false>(params, tiles, mpad, stream);
+    return tmem_a ? launch_umma_family<1, true, false>(params, tiles, mpad, stream)
+                  : launch_umma_family<1, false, false>(params, tiles, mpad, stream);
 }
 
 }  // namespace mt

@@ -72,7 +72,7 @@ static int run_projection(const void* x, const AffineWeights& first, const Affin
     for (int m0 = 0; m0 < M; m0 += 128) {
         const int rows = M - m0 < 128 ? M - m0 : 128;
         const int rc = launch_umma(xp + (size_t)m0 * K, &first, second, rp ? rp + (size_t)m0 * N : nullptr,
-                                   op + (size_t)m0 * N, rows, K, N, tmem_a, sms, stream);
+                                   op + (size_t)m0 * N, rows, K, N, tmem_a, stream);
         if (rc != MT_OK) return rc;
     }
     return MT_OK;
@@ -143,6 +143,9 @@ const char* mt_status_string(int status) {
         default: return "unknown status";
     }
 }
+
+// Diagnostic hook (not part of the public header): phase stamps of the tcgen05 kernel.
+void mt_debug_set_timeline(void* device_buffer) { g_timeline_buffer = static_cast<long long*>(device_buffer); }
 
 int mt_device_check(void) { return device_is_sm100() ? MT_OK : MT_ERR_DEVICE; }
 

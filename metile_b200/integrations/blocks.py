@@ -1,0 +1,177 @@
+"""torch modules that carry MLX-format INT4 weights: the structural targets of the patcher.
+
+They mirror what the reference patches inside MLX-LM models (metile/integrations/mlx_lm.py):
+`QuantizedLinear` (MLX's nn.QuantizedLinear: weight / scales / biases, group_size, bits, mode),
+an RMSNorm, a gated MLP with gate_proj / up_proj / down_proj, a decoder block with
+input_layernorm / self_attn / post_attention_layernorm / mlp, and a small causal LM used to verify
+logits before and after patching.  Every INT4 projection runs the CUDA kernels; none has a CPU
+path.  The UNPATCHED forward of each module is the op-by-op form native MLX computes
+(metile/backends/mlx_quantized.py:883-917: each projection rounded to bf16, then silu(gate)*up,
+then down, then the residual add), so that patching reproduces the reference's situation: the
+fused path keeps fp32 intermediates and can differ from the op-by-op path by rounding.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from .. import backends
+
+
+class QuantizedLinear(nn.Module):
+    """y = x @ dequant(weight)^T (+ bias) with MLX affine INT4 weights."""
+
+    def __init__(self, weight, scales, biases, *, group_size=64, bits=4, bias=None, mode="affine"):
+        super().__init__()
+        self.register_buffer("weight", weight)
+        self.register_buffer("scales", scales)
+        self.register_buffer("biases", biases)
+        self.group_size = group_size
+        self.bits = bits
+        self.mode = mode
+        if bias is not None:
+            self.register_buffer("bias", bias)
+        else:
+            self.bias = None
+
+    @property
+    def in_features(self):
+        return self.weight.shape[1] * 32 // self.bits
+
+    @property
+    def out_features(self):
+        return self.weight.shape[0]
+
+    @classmethod
+    def from_seed(cls, seed, in_features, out_features, device="cpu"):
+        from .. import synth
+
+        return cls(*synth.affine_weight(seed, out_features, in_features, device))
+
+    def forward(self, values):
+        out = backends.mlx_affine_qmv(values, self.weight, self.scales, self.biases,
+                                      group_size=self.group_size, bits=self.bits)
+        return out if self.bias is None else out + self.bias
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, weight, eps=1e-6):
+        super().__init__()
+        self.register_buffer("weight", weight)
+        self.eps = eps
+
+    def forward(self, values):
+        # Op-by-op reference form in torch (float32 inside, one rounding at the end).
+        v = values.float()
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()).to(values.dtype)
+
+
+class GatedMLP(nn.Module):
+    """down_proj(silu(gate_proj(x)) * up_proj(x)), each op rounded to the activation dtype."""
+
+    def __init__(self, gate_proj, up_proj, down_proj):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = gate_proj, up_proj, down_proj
+
+    def forward(self, values):
+        return self.down_proj(nn.functional.silu(self.gate_proj(values)) * self.up_proj(values))
+
+
+def _rope(values, positions, theta):
+    """Rotary embedding over the last axis (half-split form); values [B, heads, T, D]."""
+    dim = values.shape[-1]
+    inverse = 1.0 / (theta ** (torch.arange(0, dim, 2, device=values.device, dtype=torch.float32) / dim))
+    angles = positions.float()[:, None] * inverse[None, :]
+    cos, sin = angles.cos()[None, None], angles.sin()[None, None]
+    first, second = values.float()[..., : dim // 2], values.float()[..., dim // 2:]
+    return torch.cat([first * cos - second * sin, second * cos + first * sin], dim=-1).to(values.dtype)
+
+
+class Attention(nn.Module):
+    """Grouped-query attention over INT4 q/k/v/o projections with RoPE and an append-only KV cache."""
+
+    def __init__(self, q_proj, k_proj, v_proj, o_proj, heads, kv_heads, head_dim, rope_theta=1e6):
+        super().__init__()
+        self.q_proj, self.k_proj, self.v_proj, self.o_proj = q_proj, k_proj, v_proj, o_proj
+        self.heads, self.kv_heads, self.head_dim, self.rope_theta = heads, kv_heads, head_dim, rope_theta
+
+    def forward(self, values, cache=None):
+        batch, steps, _ = values.shape
+        q = self.q_proj(values).view(batch, steps, self.heads, self.head_dim).transpose(1, 2)
+        k = self.k_proj(values).view(batch, steps, self.kv_heads, self.head_dim).transpose(1, 2)
+        v = self.v_proj(values).view(batch, steps, self.kv_heads, self.head_dim).transpose(1, 2)
+        offset = 0 if cache is None or "k" not in cache else cache["k"].shape[2]
+        if steps > 1 and offset > 0:
+            raise ValueError("multi-token continuation is not supported by this harness")
+        positions = torch.arange(offset, offset + steps, device=values.device)
+        q, k = _rope(q, positions, self.rope_theta), _rope(k, positions, self.rope_theta)
+        if cache is not None:
+            if "k" in cache:
+                k = torch.cat([cache["k"], k], dim=2)
+                v = torch.cat([cache["v"], v], dim=2)
+            cache["k"], cache["v"] = k, v
+        out = nn.functional.scaled_dot_product_attention(q, k, v, is_causal=steps > 1 and offset == 0,
+                                                         enable_gqa=self.heads != self.kv_heads)
+        return self.o_proj(out.transpose(1, 2).reshape(batch, steps, self.heads * self.head_dim))
+
+
+class DecoderBlock(nn.Module):
+    """Pre-norm decoder block: x + attn(norm(x)), then h + mlp(norm(h))."""
+
+    def __init__(self, input_layernorm, self_attn, post_attention_layernorm, mlp):
+        super().__init__()
+        self.input_layernorm, self.self_attn = input_layernorm, self_attn
+        self.post_attention_layernorm, self.mlp = post_attention_layernorm, mlp
+
+    def forward(self, values, cache=None):
+        hidden = values + self.self_attn(self.input_layernorm(values), cache)
+        return hidden + self.mlp(self.post_attention_layernorm(hidden))
+
+
+class TinyCausalLM(nn.Module):
+    """Embedding, a stack of DecoderBlocks, final norm and an INT4 lm_head; random initialisation."""
+
+    def __init__(self, embed, layers, norm, lm_head, vocab_size):
+        super().__init__()
+        self.embed_tokens = embed
+        self.layers = nn.ModuleList(layers)
+        self.norm = norm
+        self.lm_head = lm_head
+        self.vocab_size = vocab_size
+
+    def make_cache(self):
+        return [{} for _ in self.layers]
+
+    def forward(self, tokens, cache=None):
+        hidden = self.embed_tokens(tokens)
+        for index, layer in enumerate(self.layers):
+            hidden = layer(hidden, None if cache is None else cache[index])
+        return self.lm_head(self.norm(hidden))
+
+
+def random_model(seed=0, *, hidden=256, intermediate=512, heads=4, kv_heads=2, head_dim=64, layers=2, vocab=512,
+                 rope_theta=1e6, eps=1e-6, device="cuda"):
+    """A seeded random-init decoder-only model in the Qwen2.5 / Llama layout with 4-bit projections."""
+    from .. import synth
+
+    def linear(offset, fan_in, fan_out):
+        return QuantizedLinear.from_seed(seed * 1000 + offset, fan_in, fan_out, device)
+
+    blocks = []
+    for index in range(layers):
+        base = 10 * index
+        attention = Attention(linear(base + 1, hidden, heads * head_dim), linear(base + 2, hidden, kv_heads * head_dim),
+                              linear(base + 3, hidden, kv_heads * head_dim), linear(base + 4, heads * head_dim, hidden),
+                              heads, kv_heads, head_dim, rope_theta)
+        mlp = GatedMLP(linear(base + 5, hidden, intermediate), linear(base + 6, hidden, intermediate),
+                       linear(base + 7, intermediate, hidden))
+        blocks.append(DecoderBlock(RMSNorm(synth.norm_weight(seed * 1000 + base + 8, hidden, device), eps), attention,
+                                   RMSNorm(synth.norm_weight(seed * 1000 + base + 9, hidden, device), eps), mlp))
+    generator = torch.Generator().manual_seed(seed * 1000 + 999)
+    table = (torch.randn((vocab, hidden), generator=generator) / math.sqrt(hidden) * 4).to(torch.bfloat16)
+    embed = nn.Embedding.from_pretrained(table.to(device), freeze=True)
+    return TinyCausalLM(embed, blocks, RMSNorm(synth.norm_weight(seed * 1000 + 998, hidden, device), eps),
+                        linear(997, hidden, vocab), vocab)

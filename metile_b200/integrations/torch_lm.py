@@ -1,0 +1,249 @@
+"""Reversible patching of torch models whose layers carry MLX-format INT4 weights.
+
+torch-side equivalent of the reference's MLX-LM patcher (metile/integrations/mlx_lm.py):
+  * apply_metile_to_torch_lm(...) -> TorchPatch       (apply_metile_to_mlx_lm, :4500-4699)
+  * TorchPatch.restore() / context manager             (MLXPatch, :305-333)
+  * class-level replacement of `forward`, the replacement carrying `_metile_original`
+    (:3791, :3927), admitted by structure (:186-237) and gated per call (:3805-3834)
+  * fused decoder block: attention, fused add+RMSNorm, then down(swiglu(norm)) + hidden
+    (:3689-3785, decision table in the same function)
+
+What differs on purpose: there is no tournament and no silent rerouting to a "native wins"
+choice.  A call the kernels cannot serve (wrong format, dtype, device, an additive bias) runs the
+module's ORIGINAL forward, and the reason is recorded once in `TorchPatch.refusals`, which
+`metile_b200.compile` copies into its report.
+"""
+
+from __future__ import annotations
+
+import weakref
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import backends
+
+FEATURES = ("attention", "rms_norm", "graph_fusion", "quantized_mlp")
+_GATED_MLP_ATTRIBUTES = ("gate_proj", "up_proj", "down_proj")
+_FUSED_BLOCK_ATTRIBUTES = ("input_layernorm", "post_attention_layernorm", "mlp")
+
+
+@dataclass
+class TorchPatch:
+    """A reversible set of class-level `forward` replacements."""
+
+    replacements: list = field(default_factory=list)
+    refusals: dict = field(default_factory=dict)
+
+    def restore(self):
+        for owner, name, original in reversed(self.replacements):
+            setattr(owner, name, original)
+        self.replacements.clear()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        self.restore()
+
+    def refuse(self, surface, reason):
+        self.refusals.setdefault(surface, reason)
+
+
+def _model_layers(model):
+    inner = getattr(model, "model", model)
+    layers = getattr(inner, "layers", None)
+    return list(layers) if layers is not None else []
+
+
+def _structurally_matches(cls, required):
+    """A class is a candidate when it defines its own forward and its instances carry the parts."""
+    return any("forward" in vars(klass) for klass in cls.__mro__ if klass is not torch.nn.Module)
+
+
+def _has_parts(module, required):
+    return all(getattr(module, name, None) is not None for name in required)
+
+
+def _is_affine_int4(linear):
+    return (
+        getattr(linear, "mode", None) == "affine"
+        and getattr(linear, "group_size", None) == 64
+        and getattr(linear, "bits", None) == 4
+        and getattr(linear, "weight", None) is not None
+        and getattr(linear, "scales", None) is not None
+        and getattr(linear, "biases", None) is not None
+    )
+
+
+def quantized_mlp_refusal(module, values):
+    """None when the fused INT4 MLP can serve this call, else the reason it cannot.
+
+    Mirrors _supports_quantized_mlp / _supports_quantized_residual_mlp of the reference
+    (metile/integrations/mlx_lm.py:3805-3834): three affine 4-bit group-64 projections with
+    quantisation biases and no additive bias; activations in the kernels' dtype (bfloat16 here,
+    float16 there) on a CUDA device.
+    """
+    for name in _GATED_MLP_ATTRIBUTES:
+        linear = getattr(module, name, None)
+        if linear is None:
+            return f"{name} is missing"
+        if not _is_affine_int4(linear):
+            return f"{name} is not an affine 4-bit group-64 quantized projection"
+        if getattr(linear, "bias", None) is not None:
+            return f"{name} has an additive bias"
+    if values.dtype != torch.bfloat16:
+        return f"activations are {values.dtype}, the kernels take bfloat16"
+    if not values.is_cuda:
+        return "activations are not on a CUDA device"
+    gate, up, down = module.gate_proj, module.up_proj, module.down_proj
+    if gate.weight.shape != up.weight.shape or down.weight.shape[0] != values.shape[-1]:
+        return "projection shapes do not form gate|up -> down"
+    return None
+
+
+_executor_cache = weakref.WeakKeyDictionary()
+
+
+def execute_quantized_mlp(module, values, residual=None):
+    """down(swiglu(values)) (+ residual) through one bound executor per module.
+
+    The executor is cached per module and dropped with it (the reference keys its cache by module
+    id with weakref eviction, metile/integrations/mlx_lm.py:3854-3885)."""
+    execute = _executor_cache.get(module)
+    if execute is None:
+        gate, up, down = module.gate_proj, module.up_proj, module.down_proj
+        execute = backends.mlx_affine_mlp_executor(
+            values, gate.weight, gate.scales, gate.biases, up.weight, up.scales, up.biases, down.weight,
+            down.scales, down.biases, None)
+        _executor_cache[module] = execute
+    return execute(values, residual)
+
+
+def _replace_forward(patch, cls, make_replacement):
+    original = cls.forward
+    if getattr(original, "_metile_original", None) is not None:
+        return False
+    replacement = make_replacement(original)
+    replacement._metile_original = original
+    patch.replacements.append((cls, "forward", original))
+    cls.forward = replacement
+    return True
+
+
+def _patch_quantized_mlp(model, patch, min_rows=1, max_rows=None):
+    if min_rows < 1:
+        raise ValueError("quantized MLP minimum rows must be positive")
+    if max_rows is not None and max_rows < min_rows:
+        raise ValueError("quantized MLP maximum rows must not be smaller than its minimum")
+    classes = [type(layer.mlp) for layer in _model_layers(model) if getattr(layer, "mlp", None) is not None]
+    for mlp_class in dict.fromkeys(classes):
+        if not _structurally_matches(mlp_class, _GATED_MLP_ATTRIBUTES):
+            continue
+
+        def make(original):
+            def replacement(self, values):
+                rows = values.numel() // values.shape[-1]
+                if rows < min_rows or (max_rows is not None and rows > max_rows):
+                    return original(self, values)
+                reason = quantized_mlp_refusal(self, values) if _has_parts(self, _GATED_MLP_ATTRIBUTES) \
+                    else "the module lacks gate_proj / up_proj / down_proj"
+                if reason is not None:
+                    patch.refuse("quantized_mlp", reason)
+                    return original(self, values)
+                return execute_quantized_mlp(self, values)
+
+            return replacement
+
+        _replace_forward(patch, mlp_class, make)
+
+
+def _norm_eps(norm):
+    for name in ("eps", "variance_epsilon"):
+        if hasattr(norm, name):
+            return float(getattr(norm, name))
+    return None
+
+
+def _patch_rms_norm(model, patch):
+    classes = []
+    for layer in _model_layers(model):
+        for name in ("input_layernorm", "post_attention_layernorm"):
+            norm = getattr(layer, name, None)
+            if norm is not None:
+                classes.append(type(norm))
+    final = getattr(getattr(model, "model", model), "norm", None)
+    if final is not None:
+        classes.append(type(final))
+    for norm_class in dict.fromkeys(classes):
+        if not _structurally_matches(norm_class, ("weight",)):
+            continue
+
+        def make(original):
+            def replacement(self, values):
+                eps = _norm_eps(self)
+                weight = getattr(self, "weight", None)
+                if eps is None or weight is None or values.dtype != torch.bfloat16 or not values.is_cuda \
+                        or weight.dtype != values.dtype:
+                    patch.refuse("rms_norm", "the norm has no weight/eps or is not bfloat16 on CUDA")
+                    return original(self, values)
+                return backends.mlx_rms_norm(values, weight, eps)
+
+            return replacement
+
+        _replace_forward(patch, norm_class, make)
+
+
+def _patch_graph_fusion(model, patch, quantized_mlp):
+    classes = [type(layer) for layer in _model_layers(model)]
+    for block_class in dict.fromkeys(classes):
+        if not _structurally_matches(block_class, _FUSED_BLOCK_ATTRIBUTES):
+            continue
+
+        def make(original):
+            def replacement(self, values, *args, **kwargs):
+                attention = getattr(self, "self_attn", None)
+                post = getattr(self, "post_attention_layernorm", None)
+                eps = _norm_eps(post) if post is not None else None
+                if attention is None or not _has_parts(self, _FUSED_BLOCK_ATTRIBUTES) or eps is None:
+                    patch.refuse("graph_fusion", "the block does not bind self_attn and two RMSNorms with eps")
+                    return original(self, values, *args, **kwargs)
+                if values.dtype != torch.bfloat16 or not values.is_cuda:
+                    patch.refuse("graph_fusion", "activations are not bfloat16 on a CUDA device")
+                    return original(self, values, *args, **kwargs)
+                attended = attention(self.input_layernorm(values), *args, **kwargs)
+                hidden, normalized = backends.mlx_add_rms_norm(values, attended, post.weight, eps)
+                if quantized_mlp:
+                    reason = quantized_mlp_refusal(self.mlp, normalized)
+                    if reason is None:
+                        return execute_quantized_mlp(self.mlp, normalized, hidden)
+                    patch.refuse("quantized_mlp", reason)
+                return hidden + self.mlp(normalized)
+
+            return replacement
+
+        _replace_forward(patch, block_class, make)
+
+
+def apply_metile_to_torch_lm(model=None, *, attention=False, rms_norm=True, graph_fusion=True,
+                             quantized_mlp=True, quantized_mlp_min_rows=1, quantized_mlp_max_rows=None):
+    """Patch the classes `model`'s layers use and return the reversible handle.
+
+    attention: decode attention has no kernel in this package; asking for it is recorded as a refusal.
+    rms_norm: RMSNorm modules run the CUDA RMSNorm.
+    graph_fusion: decoder blocks run attention, then the fused residual add + RMSNorm, then (with
+        quantized_mlp) the fused INT4 MLP with the residual folded into the down projection.
+    quantized_mlp: gated MLP modules run gate|up SwiGLU -> down as two kernels behind one call.
+    """
+    if model is None:
+        raise ValueError("apply_metile_to_torch_lm needs the model whose classes are to be patched")
+    patch = TorchPatch()
+    if attention:
+        patch.refuse("attention", "no decode-attention kernel in this package; the model's own attention runs")
+    if graph_fusion:
+        _patch_graph_fusion(model, patch, quantized_mlp)
+    if quantized_mlp:
+        _patch_quantized_mlp(model, patch, quantized_mlp_min_rows, quantized_mlp_max_rows)
+    if rms_norm:
+        _patch_rms_norm(model, patch)
+    return patch
