@@ -6,13 +6,6 @@ The operator entry points keep the reference's names and argument order
 equivalent of `metile.compile`.
 """
 
+from .compile import CompileReport, compile  # noqa: E402,F401  (the function shadows the submodule name)
+
 __all__ = ["compile", "CompileReport"]
-
-
-def __getattr__(name):
-    if name in ("compile", "CompileReport"):
-        import importlib
-
-        module = importlib.import_module(".compile", __name__)
-        return getattr(module, name)
-    raise AttributeError(name)

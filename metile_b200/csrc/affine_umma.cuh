@@ -68,7 +68,11 @@ struct UmmaConfig {
     static constexpr int kBBytes = kMPad * 128;
     static constexpr int kAbBytes = kABytes + kBBytes;
     static constexpr int kAbStages = kTmemA ? 4 : kDepth;
-    static constexpr int kAccCols = kT * kMPad;
+    // One accumulator per tile.  Measured on B200: a tcgen05.mma with M=128, K=16 costs ~45 cycles
+    // for any N <= 64 (64 for N=128, 128 for N=256) whether or not consecutive instructions share an
+    // accumulator, so splitting the K steps over several accumulators buys nothing.
+    static constexpr int kAcc = 1;
+    static constexpr int kAccCols = kT * kAcc * kMPad;
     static constexpr int kATmemCols = kTmemA ? kAbStages * kT * 32 : 0;
     static constexpr int kTmemCols = pow2_at_least(kAccCols + kATmemCols);
     // One CTA per SM (18 warps).  The ring takes what shared memory is left, up to 8 slots.
@@ -86,6 +90,7 @@ struct UmmaConfig {
     static constexpr int kDataBytes = kDataBytesMin < kFloorBytes ? kFloorBytes : kDataBytesMin;
     static constexpr int kBarrierBytes = 8 * (2 * kStages + 2 * kAbStages + 1) + 16;
     static constexpr int kSmemBytes = 1024 + kDataBytes + kBarrierBytes;
+    static_assert(kTmemCols <= 512, "tensor memory budget");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
     static_assert(kSlotBytes % 1024 == 0 && kAbBytes % 1024 == 0, "1024 B alignment");
     static_assert(2 * kSmemBytes > 227 * 1024, "a second CTA must not fit beside this one");
@@ -122,10 +127,21 @@ __device__ __forceinline__ void dequant_word_bf16(uint32_t w, __nv_bfloat162 sca
     const __nv_bfloat162 k128 = bits_bf162(0x43004300u);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t v = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;  // bf16 pair (128+q_i, 128+q_{i+4})
+        // (x & mask) | magic as ONE lop3 (truth table 0xEA) with both constants in registers; written
+        // as C the compiler emits two instructions because only one operand may be an immediate.
+        uint32_t v;  // bf16 pair (128+q_i, 128+q_{i+4})
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(w >> (4 * i)), "r"(0x000F000Fu), "r"(0x43004300u));
         const __nv_bfloat162 q = __hsub2(bits_bf162(v), k128);            // exact: integers 0..15
         out[i] = bf162_bits(__hfma2(q, scale2, bias2));                   // RN_bf16(scale*q + bias)
     }
+}
+
+// volatile: a plain __ldg may be sunk by the compiler to its first use, which would turn the
+// one-iteration-ahead prefetch of scales and biases into a load on the critical path.
+__device__ __forceinline__ uint32_t ldg_nc_u16(const uint16_t* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
 }
 
 __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
@@ -137,10 +153,14 @@ __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
 }
 
 // Diagnostic phase stamps (cycle counter of block 0's SM); a null pointer disables them.
+#ifdef MT_TIMELINE
 #define MT_STAMP(slot)                                                      \
     do {                                                                    \
         if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[slot] = clock64(); \
     } while (0)
+#else
+#define MT_STAMP(slot) do { } while (0)
+#endif
 
 template <int kT, int kMPad, bool kTmemA, bool kSwiglu>
 __global__ void __launch_bounds__(UmmaConfig<kT, kMPad, kTmemA>::kThreads, 1)
@@ -199,6 +219,10 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) MT_STAMP(1);
+    // Programmatic dependent launch: the next kernel of the stream may begin its own set-up and
+    // weight prefetch while this one is still running.  Only the weights (which no kernel writes)
+    // are touched before griddep_wait(); activations, residual and outputs come after it.
+    ptx::griddep_launch_dependents();
 
     if (warp == Cfg::kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
@@ -231,31 +255,45 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::umma_idesc_bf16(kUmmaTileRows, kMPad);
-            for (int i = 0; i < nkb; ++i) {
-                const int a = i % Cfg::kAbStages;
-                const uint32_t phase = (i / Cfg::kAbStages) & 1;
-                if (!ptx::mbar_wait(&ab_full[a], phase, abort_flag, kWaitAbFull)) break;
-                if (i == 0) MT_STAMP(7);
-                ptx::tc_fence_after_sync();
-                const uint32_t b_addr = ptx::smem_u32(ab + a * Cfg::kAbBytes + Cfg::kABytes);
+            // This one thread issues every MMA, so its loop is kept to a few instructions per MMA:
+            // the operand descriptor of byte 0 of the operand area is built once and every other
+            // descriptor is that value plus a compile-time offset (the start-address field counts
+            // 16-byte units and never carries out of its 14 bits), and the loop over k-blocks is
+            // unrolled by the number of operand stages so that stage indices are constants.
+            const uint64_t desc0 = ptx::smem_desc_k_major_sw128(ptx::smem_u32(ab));
+            for (int i0 = 0; i0 < nkb; i0 += Cfg::kAbStages) {
+                const uint32_t phase = (i0 / Cfg::kAbStages) & 1;
+                const uint32_t later = i0 > 0 ? 1u : 0u;
 #pragma unroll
-                for (int t = 0; t < kT; ++t) {
+                for (int a = 0; a < Cfg::kAbStages; ++a) {
+                    const int i = i0 + a;
+                    if (i >= nkb) break;
+                    if (!ptx::mbar_wait(&ab_full[a], phase, abort_flag, kWaitAbFull)) { i0 = nkb; break; }
+                    if (i == 0) MT_STAMP(7);
+                    if (i < 32) MT_STAMP(32 + i);
+                    ptx::tc_fence_after_sync();
 #pragma unroll
                     for (int ks = 0; ks < kUmmaBlockK / 16; ++ks) {
-                        const uint32_t d_tmem = tmem_base + t * kMPad;
-                        const uint64_t b_desc = ptx::smem_desc_k_major_sw128(b_addr + ks * 32);
-                        const uint32_t accumulate = (i > 0 || ks > 0) ? 1u : 0u;
-                        if constexpr (kTmemA) {
-                            const uint32_t a_tmem = tmem_base + Cfg::kAccCols + (a * kT + t) * 32 + ks * 8;
-                            ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
-                        } else {
-                            const uint32_t a_addr = ptx::smem_u32(ab + a * Cfg::kAbBytes + t * Cfg::kATileBytes);
-                            ptx::umma_ss(d_tmem, ptx::smem_desc_k_major_sw128(a_addr + ks * 32), b_desc, idesc,
-                                         accumulate);
+#pragma unroll
+                        for (int t = 0; t < kT; ++t) {
+                            const int chain = ks % Cfg::kAcc;
+                            const uint32_t d_tmem = tmem_base + (t * Cfg::kAcc + chain) * kMPad;
+                            const uint64_t b_desc =
+                                desc0 + (uint64_t)((a * Cfg::kAbBytes + Cfg::kABytes + ks * 32) >> 4);
+                            const uint32_t accumulate = (a > 0 || ks >= Cfg::kAcc) ? 1u : later;
+                            if constexpr (kTmemA) {
+                                const uint32_t a_tmem = tmem_base + Cfg::kAccCols + (a * kT + t) * 32 + ks * 8;
+                                ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                            } else {
+                                const uint64_t a_desc =
+                                    desc0 + (uint64_t)((a * Cfg::kAbBytes + t * Cfg::kATileBytes + ks * 32) >> 4);
+                                ptx::umma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
+                            }
                         }
                     }
+                    ptx::umma_commit(&ab_empty[a]);
+                    if (i < 32) MT_STAMP(64 + i);
                 }
-                ptx::umma_commit(&ab_empty[a]);
             }
             ptx::umma_commit(acc_full);
             MT_STAMP(8);
@@ -288,10 +326,11 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
             }
         };
         if (depth < nkb) {
-            scale_next = __ldg(scale_row + depth);
-            bias_next = __ldg(bias_row + depth);
-            load_x(depth);
+            scale_next = ldg_nc_u16(scale_row + depth);
+            bias_next = ldg_nc_u16(bias_row + depth);
         }
+        ptx::griddep_wait();  // everything below may read what the preceding kernel wrote
+        if (depth < nkb) load_x(depth);
         bool alive = true;
         for (int st = 0; st < nslots && alive; ++st) {
             const int s = st % Cfg::kStages;
@@ -303,14 +342,12 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 const int j = depth + jj * Cfg::kDepth;              // k-block inside the slot
                 const int i = st * kUmmaKBlocksPerSlot + j;          // k-block inside this CTA's range
                 if (i >= nkb) break;
-                const bool probe = (p.timeline != nullptr && blockIdx.x == 0 && i == 8 && threadIdx.x == 32);
-                if (probe) MT_STAMP(16);
                 const int a = i % Cfg::kAbStages;
                 const uint32_t aphase = (i / Cfg::kAbStages) & 1;
                 const uint32_t scale_bits = scale_next, bias_bits = bias_next;
                 if (i + Cfg::kDepth < nkb) {
-                    scale_next = __ldg(scale_row + i + Cfg::kDepth);
-                    bias_next = __ldg(bias_row + i + Cfg::kDepth);
+                    scale_next = ldg_nc_u16(scale_row + i + Cfg::kDepth);
+                    bias_next = ldg_nc_u16(bias_row + i + Cfg::kDepth);
                 }
                 uint4 xv[kXTasks];
 #pragma unroll
@@ -321,11 +358,9 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                     waited = true;
                     if (st == 0 && threadIdx.x == 0) MT_STAMP(4);
                 }
-                if (probe) MT_STAMP(17);
                 if (!ptx::mbar_wait(&ab_empty[a], aphase ^ 1, abort_flag, kWaitAbEmpty)) { alive = false; break; }
                 __syncwarp();  // the .sync.aligned tcgen05 instructions below need a converged warp
                 ptx::tc_fence_after_sync();
-                if (probe) MT_STAMP(18);
 
                 // 32 B of this row for k-block j: 16-byte chunks 2j and 2j+1, XOR-swizzled by the row.
                 const uint8_t* wrow = slot + t * Cfg::kWTileBytes + r * 128;
@@ -339,7 +374,6 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 for (int c = 0; c < 8; ++c) dequant_word_bf16(words[c], scale2, bias2, &wq[4 * c]);
 
                 uint8_t* ab_stage = ab + a * Cfg::kAbBytes;
-                if (probe) p.timeline[19] = clock64() + (wq[31] & 1);
                 if constexpr (kTmemA) {
                     const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + Cfg::kAccCols +
                                             (a * kT + t) * 32;
@@ -368,21 +402,17 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                         *reinterpret_cast<uint4*>(b_tile + row * 128 + ((c ^ (row & 7)) << 4)) = o;
                     }
                 }
-                if (probe) MT_STAMP(20);
                 // One cross-proxy fence covers both directions: the tiles written above become visible
                 // to the MMA (async proxy), and the ring slot read above with ordinary loads may later be
                 // overwritten by TMA (async proxy).  Releasing a slot without such a fence was observed
                 // to let the refill overtake the reads.
                 ptx::fence_proxy_async_smem();
-                if (probe) MT_STAMP(21);
                 if constexpr (kTmemA) {
                     ptx::tc_wait_st();
                     ptx::tc_fence_before_sync();
                 }
-                if (probe) MT_STAMP(22);
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&ab_full[a]);
-                if (probe) MT_STAMP(23);
                 if (i == 0 && threadIdx.x == 0) MT_STAMP(5);
             }
             if (!alive) break;
@@ -408,17 +438,24 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
             float* staging = reinterpret_cast<float*>(smem);
 #pragma unroll
             for (int c0 = 0; c0 < kMPad; c0 += 16) {
-                uint32_t v[16];
-                if (ok) {
-                    ptx::tmem_ld16(tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + t * kMPad + c0, v);
-                    ptx::tc_wait_ld();
-                } else {
+                float v[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0u;
+                for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                if (ok) {
+#pragma unroll
+                    for (int chain = 0; chain < Cfg::kAcc; ++chain) {
+                        uint32_t part[16];
+                        ptx::tmem_ld16(tmem_base + ((uint32_t)((warp & 3) << 5) << 16) +
+                                           (t * Cfg::kAcc + chain) * kMPad + c0, part);
+                        ptx::tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            v[j] = chain == 0 ? __uint_as_float(part[j]) : v[j] + __uint_as_float(part[j]);
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    if (c0 + j < p.M) staging[(t * kMPad + c0 + j) * kUmmaTileRows + r] = __uint_as_float(v[j]);
+                    if (c0 + j < p.M) staging[(t * kMPad + c0 + j) * kUmmaTileRows + r] = v[j];
             }
             if (threadIdx.x == 0) MT_STAMP(10);
         }
@@ -579,13 +616,15 @@ inline int launch_umma_instance(const UmmaParams& params, int tiles, cudaStream_
     config.blockDim = dim3(Cfg::kThreads, 1, 1);
     config.dynamicSmemBytes = Cfg::kSmemBytes;
     config.stream = stream;
-    cudaLaunchAttribute attrs[1];
+    cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = params.ksplit;
     attrs[0].val.clusterDim.y = 1;
     attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attrs;
-    config.numAttrs = 1;
+    config.numAttrs = 2;
     return cudaLaunchKernelEx(&config, affine_umma_kernel<kT, kMPad, kTmemA, kSwiglu>, params) == cudaSuccess
                ? MT_OK
                : MT_ERR_LAUNCH;

@@ -54,14 +54,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
+// try_wait with a suspend-time hint: the hardware may park the thread for up to `hint_ns` until the
+// phase completes, instead of returning at once.  A parked warp takes no issue slots away from the
+// warps that are working, which matters here: eighteen warps share four schedulers.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return done != 0;
+}
+
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the whole CTA.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned int code) {
-    for (int spin = 0; spin < 4096; ++spin)
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
+    for (int spin = 0; spin < 64; ++spin)
+        if (mbar_try_wait_hint(bar, parity, 100000u)) return true;
     const unsigned long long start = global_timer_ns();
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_hint(bar, parity, 100000u)) return true;
         if (*abort_flag) return false;
         if (global_timer_ns() - start > kWaitLimitNs) {
             if (atomicCAS(&g_device_status[0], 0u, code) == 0u) {
@@ -72,7 +88,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             *abort_flag = 1;
             return false;
         }
-        __nanosleep(64);
     }
 }
 
@@ -181,6 +196,15 @@ __device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addr) 
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+
+// ---- programmatic dependent launch ----------------------------------------------------------
+// launch_dependents: the next kernel in the stream (if launched with the programmatic-serialization
+// attribute) may start once every CTA of this grid has executed this or exited.
+// wait: blocks until the preceding grid has completed and its memory is visible.
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- cluster -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {

@@ -1,0 +1,244 @@
+"""CPU tests of the patcher and of `compile`: report semantics, structural admission, restore,
+per-call refusal, bisecting.  The CUDA operators are replaced by torch stand-ins, in the way the
+reference's patcher tests replace kernels with recording fakes
+(tests/test_mlx_backend.py:3184-3558, tests/test_compile.py:18-94 of the reference)."""
+
+import pytest
+import torch
+from torch import nn
+
+import metile_b200
+from metile_b200 import backends
+from metile_b200.compile import CompileReport
+from metile_b200.integrations import torch_lm
+
+
+class FakeQuantizedLinear(nn.Module):
+    """Carries the attributes the support gate inspects; computes with a dense float weight."""
+
+    def __init__(self, fan_in, fan_out, seed, bias=False, bits=4):
+        super().__init__()
+        generator = torch.Generator().manual_seed(seed)
+        self.dense = (torch.randn((fan_out, fan_in), generator=generator) / fan_in ** 0.5).to(torch.bfloat16)
+        self.weight = torch.zeros((fan_out, fan_in // 8), dtype=torch.int32)
+        self.scales = torch.ones((fan_out, fan_in // 64), dtype=torch.bfloat16)
+        self.biases = torch.zeros((fan_out, fan_in // 64), dtype=torch.bfloat16)
+        self.group_size, self.bits, self.mode = 64, bits, "affine"
+        self.bias = torch.zeros(fan_out, dtype=torch.bfloat16) if bias else None
+
+    def forward(self, values):
+        return (values.float() @ self.dense.float().t()).to(values.dtype)
+
+
+class FakeNorm(nn.Module):
+    def __init__(self, width):
+        super().__init__()
+        self.weight = torch.ones(width, dtype=torch.bfloat16)
+        self.eps = 1e-6
+
+    def forward(self, values):
+        v = values.float()
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()).to(values.dtype)
+
+
+class FakeMLP(nn.Module):
+    def __init__(self, width, inter, seed, **kw):
+        super().__init__()
+        self.gate_proj = FakeQuantizedLinear(width, inter, seed, **kw)
+        self.up_proj = FakeQuantizedLinear(width, inter, seed + 1, **kw)
+        self.down_proj = FakeQuantizedLinear(inter, width, seed + 2, **kw)
+
+    def forward(self, values):
+        return self.down_proj(nn.functional.silu(self.gate_proj(values)) * self.up_proj(values))
+
+
+class FakeAttention(nn.Module):
+    def forward(self, values, cache=None):
+        return values * 0.5
+
+
+class FakeBlock(nn.Module):
+    def __init__(self, width, inter, seed, **kw):
+        super().__init__()
+        self.input_layernorm, self.post_attention_layernorm = FakeNorm(width), FakeNorm(width)
+        self.self_attn, self.mlp = FakeAttention(), FakeMLP(width, inter, seed, **kw)
+
+    def forward(self, values, cache=None):
+        hidden = values + self.self_attn(self.input_layernorm(values), cache)
+        return hidden + self.mlp(self.post_attention_layernorm(hidden))
+
+
+class FakeLM(nn.Module):
+    def __init__(self, width=64, inter=128, vocab=50, layers=2, **kw):
+        super().__init__()
+        self.vocab_size = vocab
+        generator = torch.Generator().manual_seed(5)
+        self.table = torch.randn((vocab, width), generator=generator).to(torch.bfloat16)
+        self.layers = nn.ModuleList([FakeBlock(width, inter, 10 * i, **kw) for i in range(layers)])
+        self.norm = FakeNorm(width)
+        self.head = torch.randn((vocab, width), generator=generator).to(torch.bfloat16)
+
+    def make_cache(self):
+        return [None for _ in self.layers]
+
+    def forward(self, tokens, cache=None):
+        hidden = self.table[tokens]
+        for layer in self.layers:
+            hidden = layer(hidden)
+        return (self.norm(hidden).float() @ self.head.float().t())
+
+
+@pytest.fixture
+def fake_kernels(monkeypatch):
+    """torch stand-ins for the CUDA operators, recording calls; `skew` perturbs the fused MLP."""
+    calls = {"mlp": 0, "add_rms": 0, "rms": 0, "skew": 0.0}
+
+    def fake_executor(sample, gw, gs, gb, uw, us, ub, dw, ds, db, sample_residual, **_):
+        def execute(values, residual=None):
+            calls["mlp"] += 1
+            module = fake_executor.module
+            out = module.down_proj(nn.functional.silu(module.gate_proj(values)) * module.up_proj(values))
+            out = out.float() * (1.0 + calls["skew"])
+            if residual is not None:
+                out = out + residual.float()
+            return out.to(values.dtype)
+
+        return execute
+
+    def fake_execute_quantized_mlp(module, values, residual=None):
+        fake_executor.module = module
+        return fake_executor(values, *[None] * 9, None)(values, residual)
+
+    def fake_add_rms(values, residual, weight, eps, **_):
+        calls["add_rms"] += 1
+        total = values + residual
+        v = total.float()
+        return total, (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(values.dtype)
+
+    def fake_rms(values, weight, eps, **_):
+        calls["rms"] += 1
+        v = values.float()
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(values.dtype)
+
+    monkeypatch.setattr(torch_lm, "execute_quantized_mlp", fake_execute_quantized_mlp)
+    monkeypatch.setattr(backends, "mlx_add_rms_norm", fake_add_rms)
+    monkeypatch.setattr(backends, "mlx_rms_norm", fake_rms)
+    # The gate refuses CPU tensors; the fakes run on CPU, so relax only that clause.
+    original_gate = torch_lm.quantized_mlp_refusal
+
+    def cpu_gate(module, values):
+        reason = original_gate(module, values)
+        return None if reason == "activations are not on a CUDA device" else reason
+
+    monkeypatch.setattr(torch_lm, "quantized_mlp_refusal", cpu_gate)
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+    return calls
+
+
+def test_report_truthiness_and_wording():
+    empty = CompileReport(model="llama")
+    assert not empty
+    assert "accelerating: nothing" in str(empty)
+    kept = CompileReport(model="qwen2", features=("rms_norm",), surfaces=("input_layernorm",), verified=True,
+                         difference=0.0)
+    assert kept and "logits match the unpatched model exactly" in str(kept)
+    close = CompileReport(model="llama", features=("quantized_mlp",), surfaces=("mlp",), verified=True,
+                          difference=0.0352, relative=2.3e-3, declined={"attention": "no kernel"})
+    text = str(close)
+    assert "within tolerance, logits differ by 0.0352 (2.3e-03 relative)" in text
+    assert "declined attention: no kernel" in text
+    assert "skipped (verify=False)" in str(CompileReport(model="x", features=("rms_norm",), verified=None))
+    assert "FAILED, everything reverted" in str(CompileReport(model="x", verified=False))
+
+
+def test_compile_rejects_non_models():
+    with pytest.raises(TypeError):
+        metile_b200.compile(None)
+    with pytest.raises(TypeError):
+        metile_b200.compile(3)
+
+
+def test_compile_patches_verifies_and_restores(fake_kernels):
+    model = FakeLM()
+    original_block, original_mlp, original_norm = FakeBlock.forward, FakeMLP.forward, FakeNorm.forward
+    report = metile_b200.compile(model, tolerance=1e-2)
+    try:
+        assert report and report.verified is True
+        assert set(report.features) == {"rms_norm", "graph_fusion", "quantized_mlp"}
+        assert "block" in report.surfaces and "mlp" in report.surfaces
+        assert "attention" in report.declined  # asked for, no kernel: recorded, not silently dropped
+        assert FakeBlock.forward._metile_original is original_block
+        assert fake_kernels["mlp"] > 0 and fake_kernels["add_rms"] > 0 and fake_kernels["rms"] > 0
+    finally:
+        report.restore()
+    assert FakeBlock.forward is original_block and FakeMLP.forward is original_mlp
+    assert FakeNorm.forward is original_norm
+    report.restore()  # idempotent
+
+
+def test_compile_bisects_and_declines_a_wrong_surface(fake_kernels):
+    model = FakeLM()
+    fake_kernels["skew"] = 0.5  # the fused MLP now computes something else
+    report = metile_b200.compile(model, tolerance=1e-2)
+    try:
+        assert "combined" in report.declined
+        assert "quantized_mlp" in report.declined and "different computation" in report.declined["quantized_mlp"]
+        # Block fusion alone calls the module's own MLP, so it still reproduces the logits.
+        assert report.features == ("rms_norm", "graph_fusion")
+    finally:
+        report.restore()
+    assert not hasattr(FakeMLP.forward, "_metile_original")
+
+
+def test_reduction_order_scale_wording(fake_kernels):
+    model = FakeLM()
+    fake_kernels["skew"] = 2e-3
+    report = metile_b200.compile(model, tolerance=0.0, features=("quantized_mlp",))
+    try:
+        assert not report
+        assert report.verified is False
+        assert "reduction-order scale, raise tolerance to keep it" in report.declined["quantized_mlp"]
+    finally:
+        report.restore()
+
+
+def test_unsupported_projection_is_refused_per_call_not_rerouted(fake_kernels):
+    model = FakeLM(bias=True)  # additive bias: outside the kernels' format
+    report = metile_b200.compile(model, tolerance=1e-2, features=("quantized_mlp", "graph_fusion"))
+    try:
+        assert fake_kernels["mlp"] == 0  # the original forward served every call
+        assert "quantized_mlp" in report.declined and "additive bias" in report.declined["quantized_mlp"]
+        assert "quantized_mlp" not in report.features
+    finally:
+        report.restore()
+
+
+def test_model_without_replaceable_classes_reports_nothing():
+    class Plain(nn.Module):
+        vocab_size = 11
+
+        def forward(self, tokens, cache=None):
+            return torch.zeros((*tokens.shape, 11))
+
+    report = metile_b200.compile(Plain())
+    assert not report
+    assert "surfaces" in report.declined
+
+
+def test_row_gates_and_handle_context_manager(fake_kernels):
+    model = FakeLM()
+    with torch_lm.apply_metile_to_torch_lm(model, graph_fusion=False, rms_norm=False, quantized_mlp=True,
+                                           quantized_mlp_min_rows=4, quantized_mlp_max_rows=8) as patch:
+        x = torch.randn((1, 2, 64)).to(torch.bfloat16)
+        model.layers[0].mlp(x)
+        assert fake_kernels["mlp"] == 0  # 2 rows < min_rows
+        model.layers[0].mlp(torch.randn((1, 6, 64)).to(torch.bfloat16))
+        assert fake_kernels["mlp"] == 1
+        model.layers[0].mlp(torch.randn((1, 16, 64)).to(torch.bfloat16))
+        assert fake_kernels["mlp"] == 1  # 16 rows > max_rows
+        assert patch.replacements
+    assert not hasattr(FakeMLP.forward, "_metile_original")
+    with pytest.raises(ValueError):
+        torch_lm.apply_metile_to_torch_lm(model, quantized_mlp_min_rows=0)
+    with pytest.raises(ValueError):
+        torch_lm.apply_metile_to_torch_lm(None)
