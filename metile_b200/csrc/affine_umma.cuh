@@ -55,8 +55,14 @@ constexpr int pow2_at_least(int v) {
 
 template <int kT, int kMPad, bool kTmemA>
 struct UmmaConfig {
-    static constexpr int kDepth = 4 / kT;                           // dequant groups per tile
-    static constexpr int kDequantWarps = 16;                        // 4 warps x kT tiles x kDepth
+    // One footprint: 16 dequant warps, one CTA per SM.  A lighter variant (8 dequant warps, two
+    // CTAs per SM so that consecutive kernels chained by programmatic dependent launch overlap)
+    // was measured and was slower (16.2 vs 12.7 us for the 2048->8192 gate|up projection at one
+    // row): what limits a CTA is the latency of one warp's dequant iteration, so halving the
+    // warps per CTA doubled it and the overlap did not pay that back.
+    static constexpr bool kLight = false;
+    static constexpr int kDequantWarps = kLight ? 8 : 16;           // 4 warps x kT tiles x kDepth
+    static constexpr int kDepth = kDequantWarps / (4 * kT);         // dequant groups per tile
     static constexpr int kWarpsPerKBlock = 4 * kT;                  // warps that serve one k-block
     static constexpr int kProducerWarp = kDequantWarps;
     static constexpr int kMmaWarp = kDequantWarps + 1;
@@ -67,7 +73,7 @@ struct UmmaConfig {
     static constexpr int kABytes = kTmemA ? 0 : kT * kATileBytes;
     static constexpr int kBBytes = kMPad * 128;
     static constexpr int kAbBytes = kABytes + kBBytes;
-    static constexpr int kAbStages = kTmemA ? 4 : kDepth;
+    static constexpr int kAbStages = !kTmemA ? kDepth : (kLight && kT == 2 ? 3 : 4);
     // One accumulator per tile.  Measured on B200: a tcgen05.mma with M=128, K=16 costs ~45 cycles
     // for any N <= 64 (64 for N=128, 128 for N=256) whether or not consecutive instructions share an
     // accumulator, so splitting the K steps over several accumulators buys nothing.
@@ -75,8 +81,9 @@ struct UmmaConfig {
     static constexpr int kAccCols = kT * kAcc * kMPad;
     static constexpr int kATmemCols = kTmemA ? kAbStages * kT * 32 : 0;
     static constexpr int kTmemCols = pow2_at_least(kAccCols + kATmemCols);
-    // One CTA per SM (18 warps).  The ring takes what shared memory is left, up to 8 slots.
-    static constexpr int kRingTarget = 196 * 1024 - kAbStages * kAbBytes;
+    // The ring takes what shared memory the footprint leaves, up to 8 slots.
+    static constexpr int kBudgetBytes = (kLight ? 108 : 196) * 1024;
+    static constexpr int kRingTarget = kBudgetBytes - kAbStages * kAbBytes;
     static constexpr int kStagesRaw = kRingTarget / kSlotBytes;
     static constexpr int kStages = kStagesRaw < 2 ? 2 : (kStagesRaw > 8 ? 8 : kStagesRaw);
     static constexpr int kRingBytes = kStages * kSlotBytes;
@@ -84,16 +91,19 @@ struct UmmaConfig {
     static constexpr int kDataBytesRaw = kRingBytes + kAbStages * kAbBytes;
     static constexpr int kDataBytesMin = kDataBytesRaw > kStagingBytes ? kDataBytesRaw : kStagingBytes;
     // TMEM columns x resident CTAs must never exceed 512: a later CTA's tcgen05.alloc would wait
-    // for an earlier CTA to finish.  Every CTA therefore asks for more than half of an SM's
-    // shared memory, which keeps it alone on its SM.
-    static constexpr int kFloorBytes = (227 * 1024) / 2 + 2048;
+    // for an earlier CTA to finish.  Shared memory bounds residency, so every CTA asks for more
+    // than 1/(allowed+1) of an SM's shared memory.
+    static constexpr int kAllowedPerSm = kLight ? 2 : 1;
+    static constexpr int kFloorBytes = (227 * 1024) / (kAllowedPerSm + 1) + 2048;
     static constexpr int kDataBytes = kDataBytesMin < kFloorBytes ? kFloorBytes : kDataBytesMin;
     static constexpr int kBarrierBytes = 8 * (2 * kStages + 2 * kAbStages + 1) + 16;
     static constexpr int kSmemBytes = 1024 + kDataBytes + kBarrierBytes;
     static_assert(kTmemCols <= 512, "tensor memory budget");
     static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
     static_assert(kSlotBytes % 1024 == 0 && kAbBytes % 1024 == 0, "1024 B alignment");
-    static_assert(2 * kSmemBytes > 227 * 1024, "a second CTA must not fit beside this one");
+    static_assert((kAllowedPerSm + 1) * kSmemBytes > 227 * 1024, "one CTA too many would fit on an SM");
+    static_assert(kAllowedPerSm * (kSmemBytes + 1024) <= 227 * 1024, "the intended residency does not fit");
+    static_assert(kAllowedPerSm * kTmemCols <= 512, "tensor memory over-subscribed");
     static_assert(kAbStages % kDepth == 0, "each depth group owns whole operand stages");
     static_assert(kUmmaKBlocksPerSlot % kDepth == 0, "a group sees the same k-blocks in every slot");
 };
@@ -163,7 +173,7 @@ __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
 #endif
 
 template <int kT, int kMPad, bool kTmemA, bool kSwiglu>
-__global__ void __launch_bounds__(UmmaConfig<kT, kMPad, kTmemA>::kThreads, 1)
+__global__ void __launch_bounds__(UmmaConfig<kT, kMPad, kTmemA>::kThreads, UmmaConfig<kT, kMPad, kTmemA>::kAllowedPerSm)
 affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     using Cfg = UmmaConfig<kT, kMPad, kTmemA>;
     static_assert(!kSwiglu || kT == 2, "SwiGLU pairs a gate tile with an up tile");
@@ -473,10 +483,11 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     if (threadIdx.x == 0) MT_STAMP(11);
     if (warp < Cfg::kDequantWarps) {
         const int r = threadIdx.x & 127;
-        const int part = threadIdx.x >> 7;         // four groups of 128 threads share the rows
+        const int part = threadIdx.x >> 7;         // groups of 128 threads share the rows
+        constexpr int kParts = Cfg::kDequantWarps / 4;
         const int n = n0 + r;
         const uint32_t staging_addr = ptx::smem_u32(smem);
-        for (int m = rank + ksplit * part; m < p.M; m += ksplit * 4) {
+        for (int m = rank + ksplit * part; m < p.M; m += ksplit * kParts) {
             float first = 0.0f, second = 0.0f;
             if (ksplit > 1) {
                 for (int j = 0; j < ksplit; ++j) {
