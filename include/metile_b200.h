@@ -85,6 +85,31 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
                   size_t workspace_bytes, void* out, int M, int H, int I, int group_size, int bits,
                   unsigned int flags, void* stream);
 
+/* The fused MLP of mt_affine_mlp for callers that may not allocate device memory.
+ * No counterpart in the reference project.
+ * Some hosts of this library cannot call cudaMalloc on the path that runs the MLP: a serving loop
+ * that forbids allocation after start-up because cudaMalloc synchronises the whole device, a
+ * plugin that was handed a fixed arena and nothing else, or code running while a stream is being
+ * captured, where allocation calls are errors.  For them the bf16 hidden activations [M, I] live
+ * in an array compiled into the library (mt_affine_mlp_static_max_bytes() bytes, 4 MiB, held by
+ * every GPU that loads the library until the process exits) instead of a caller workspace.  Inputs
+ * and the output are still the caller's.  The call makes no cudaMalloc / cudaFree and uses no
+ * allocating library routine.
+ *   - Limit: M * I * 2 bytes must not exceed mt_affine_mlp_static_max_bytes(); larger problems are
+ *     refused with -7 before anything is queued.  Use mt_affine_mlp with your own workspace then.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call before beginning any stream capture.
+ *   - All calls share the one array and it keeps the last call's contents.  Nothing needs clearing:
+ *     each call overwrites every element it later reads.  Two calls that overlap on the GPU (two
+ *     streams, two host threads) race on the array; serialise them.
+ * Results are bit-identical to mt_affine_mlp with the same arguments. */
+size_t mt_affine_mlp_static_max_bytes(void);
+int mt_affine_mlp_static(const void* x, const uint32_t* gate_w, const void* gate_scales,
+                         const void* gate_biases, const uint32_t* up_w, const void* up_scales,
+                         const void* up_biases, const uint32_t* down_w, const void* down_scales,
+                         const void* down_biases, const void* residual, void* out, int M, int H, int I,
+                         int group_size, int bits, unsigned int flags, void* stream);
+
 /* sum_out = bf16(x + residual); norm_out = bf16(sum_out * rsqrt(mean((x+residual)^2) + eps) * w).
  * Replaces: metile/backends/mlx.py:786 (mlx_add_rms_norm), kernels/add_rmsnorm.py:5.
  * sum_out may be NULL. */

@@ -121,6 +121,29 @@ dense_act_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b,
     }
 }
 
+// Scratch for mt_affine_mlp_static: the bf16 hidden activations [M, I] of one fused MLP call.
+// It lives in the library's device image, so every GPU that loads the library holds these bytes
+// until the process exits.  In host code this name is only a handle for cudaGetSymbolAddress; the
+// device address is looked up once per device (static_hidden_address below).
+constexpr size_t kStaticHiddenBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_static_hidden[kStaticHiddenBytes];
+
+// Device address of g_static_hidden on the current device, resolved on first use per device.
+static int static_hidden_address(void** out) {
+    static void* cached[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return MT_ERR_DEVICE;
+    if (device >= 0 && device < 64 && cached[device]) {
+        *out = cached[device];
+        return MT_OK;
+    }
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, g_static_hidden) != cudaSuccess || address == nullptr) return MT_ERR_LAUNCH;
+    if (device >= 0 && device < 64) cached[device] = address;
+    *out = address;
+    return MT_OK;
+}
+
 }  // namespace mt
 
 using namespace mt;
@@ -213,6 +236,26 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
                           group_size, bits, flags, stream);
     if (rc != MT_OK) return rc;
     return mt_affine_qmv(workspace, down_w, down_scales, down_biases, residual, out, M, I, H, group_size, bits, flags,
+                         stream);
+}
+
+size_t mt_affine_mlp_static_max_bytes(void) { return kStaticHiddenBytes; }
+
+int mt_affine_mlp_static(const void* x, const uint32_t* gate_w, const void* gate_scales, const void* gate_biases,
+                         const uint32_t* up_w, const void* up_scales, const void* up_biases, const uint32_t* down_w,
+                         const void* down_scales, const void* down_biases, const void* residual, void* out, int M,
+                         int H, int I, int group_size, int bits, unsigned int flags, void* stream) {
+    if (M < 0 || H < 1 || I < 1) return MT_ERR_SHAPE;
+    if (M == 0) return MT_OK;
+    const size_t needed = (size_t)M * (size_t)I * 2;
+    if (needed > kStaticHiddenBytes) return MT_ERR_WORKSPACE;  // the hidden activations do not fit the array
+    void* scratch = nullptr;
+    const int rc = static_hidden_address(&scratch);
+    if (rc != MT_OK) return rc;
+    // Every element of hidden[0:M, 0:I] is written by the gate|up kernel before the down kernel
+    // reads it, so nothing left over from an earlier call is ever consumed and nothing is cleared.
+    return mt_affine_mlp(x, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, down_w, down_scales,
+                         down_biases, residual, scratch, kStaticHiddenBytes, out, M, H, I, group_size, bits, flags,
                          stream);
 }
 
