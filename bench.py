@@ -338,7 +338,9 @@ def run_ours(args):
             "unit": "GB/s",
             "frac": achieved / hbm_peak,
             "peak_kind": f"of {peak_kind}",
-            "traffic": None,
+            # dram__bytes_read.sum + dram__bytes_write.sum of this kernel from the ncu capture summarised in
+            # profiles/affine_gemv_swiglu_m1_llama1b.md (equals the algorithmic bytes: no re-reads).
+            "traffic": 18904832,
             "algorithmic_bytes_per_launch": int(algorithmic),
             "us_per_launch": per_launch * 1e6,
         }
