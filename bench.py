@@ -72,6 +72,33 @@ class ClockSampler:
         self._thread = threading.Thread(target=self._run, daemon=True)
 
     def _run(self):
+        try:
+            self._run_nvml()
+        except Exception:
+            self._run_smi()
+
+    def _run_nvml(self):
+        """In-process NVML queries (read-only): no fork while CUDA / NCCL threads are running."""
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        bits = {
+            "hw_slowdown": pynvml.nvmlClocksThrottleReasonHwSlowdown,
+            "hw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonHwThermalSlowdown,
+            "sw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonSwThermalSlowdown,
+            "sw_power_cap": pynvml.nvmlClocksThrottleReasonSwPowerCap,
+        }
+        while not self._stop.is_set():
+            self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+            reasons = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+            for name, bit in bits.items():
+                if reasons & bit:
+                    self.reasons.add(name)
+            self._stop.wait(0.05)
+
+    def _run_smi(self):
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         while not self._stop.is_set():
             try:
@@ -180,6 +207,12 @@ def workload_config(hidden, inter, sweep, gpus, l2_note):
     }
 
 
+def log(message):
+    """Progress on stderr (the JSON line alone goes to stdout)."""
+    if os.environ.get("RANK", "0") == "0":
+        print(f"[bench {time.strftime('%H:%M:%S')}] {message}", file=sys.stderr, flush=True)
+
+
 def run_ours(args):
     import torch
 
@@ -207,6 +240,7 @@ def run_ours(args):
     copies = max(2, -(-2 * l2_bytes // local_bytes) + 1)
     copies = min(copies, 24)
 
+    log(f"world {world}, workload hidden {hidden} / intermediate {inter}, {copies} weight sets")
     # ---- build the rotating weight sets and executors -------------------------------------------
     executors = []
     for c in range(copies):
@@ -258,20 +292,38 @@ def run_ours(args):
         torch.cuda.synchronize()
         return start.elapsed_time(stop) * 1e-3
 
+    log("weights resident; warm-up")
+    def time_eager(fn, repeats):
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(repeats):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) * 1e-3
+
     # ---- headline: K steps, each one sweep, replayed as a CUDA graph ------------------------------
+    # (single GPU).  The tensor-parallel run times eager launches instead: replaying graphs that
+    # contain NCCL collectives did not make progress on this pool, eager collectives do.
     for _ in range(3):
         sweep_once()
     torch.cuda.synchronize()
-    step_graph = capture(sweep_once, 1)
-    for _ in range(max(args.warmup, 3)):
-        step_graph.replay()
+    log("eager warm-up done; capturing the sweep")
+    if tp:
+        run_steps = lambda n: time_eager(sweep_once, n)  # noqa: E731
+    else:
+        step_graph = capture(sweep_once, 1)
+        log("graph captured")
+        run_steps = lambda n: time_graph(step_graph, n)  # noqa: E731
+    run_steps(max(args.warmup, 3))
     barrier()
     with ClockSampler(local_rank) as clocks:
-        seconds = time_graph(step_graph, args.steps)
+        seconds = run_steps(args.steps)
         barrier()
         # Keep the sampler alive long enough for a few samples when the steps are very short.
-        if seconds < 1.0:
-            filler = time_graph(step_graph, max(1, int(1.0 / max(seconds / args.steps, 1e-6))))
+        if seconds < 0.5 and not tp:
+            filler = run_steps(max(1, int(0.5 / max(seconds / args.steps, 1e-6))))
             del filler
     if distributed:
         t = torch.tensor([seconds], device=device)
@@ -281,19 +333,26 @@ def run_ours(args):
     total_bytes = per_mlp_bytes * len(sweep)
     value = total_bytes / step_seconds / 1e9
 
+    log(f"headline: {step_seconds * 1e3:.3f} ms per step")
     # ---- per-M detail (graph of 8 MLP calls per M) ------------------------------------------------
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
     detail = []
     for m in sweep:
+        log(f"detail M={m}")
         x, r = inputs[m]
 
         def one(x=x, r=r):
             next_executor()(x, r)
 
-        graph = capture(one, 8)
-        graph.replay()
-        barrier()
-        per_call = time_graph(graph, 10) / 80
+        if tp:
+            time_eager(one, 8)
+            barrier()
+            per_call = time_eager(one, 80) / 80
+        else:
+            graph = capture(one, 8)
+            graph.replay()
+            barrier()
+            per_call = time_graph(graph, 10) / 80
         if distributed:
             t = torch.tensor([per_call], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -346,6 +405,7 @@ def run_ours(args):
         }
         del gate_sets
 
+    log("per-M detail done")
     # ---- end to end through the public executor with host buffers ---------------------------------
     def e2e_step():
         for m in sweep:
@@ -356,9 +416,11 @@ def run_ours(args):
             host_outputs[m].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
+    log("e2e warm-up")
     for _ in range(3):
         e2e_step()
     barrier()
+    log("e2e timed")
     start = time.perf_counter()
     for _ in range(args.steps):
         e2e_step()
@@ -406,6 +468,7 @@ def run_ours(args):
             "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_seconds * 1e3},
             "gpu_launches": kernels_per_mlp * len(sweep) * args.steps,
+            "timing": "eager launches, CUDA events" if tp else "CUDA-graph replay, CUDA events",
             "clocks": clocks.summary(),
         }
         print(json.dumps(line))

@@ -13,7 +13,7 @@
 // (128 TMEM lanes), the activation rows (padded to 16/32/64/128) are its N dimension, K advances
 // 16 elements per instruction, 64 (one quantisation group) per pipeline step.
 //
-//   producer lane  : TMA (cp.async.bulk.tensor, no multicast, 128B swizzle) packed weight tile(s) of
+//   producer lane  : TMA (per-CTA tiled load, 128B swizzle) packed weight tile(s) of
 //                    128 rows x 128 B = four k-blocks per ring slot; boxes with a 32-byte inner
 //                    extent were measured to be limited by the TMA request rate, not by HBM
 //   dequant warps  : 16 warps in groups of four (one group = the 128 rows of one tile); with kT

@@ -1,4 +1,4 @@
-// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, never multicast),
+// Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (plain per-CTA tiled loads),
 // tcgen05 (TMEM alloc / mma / commit / ld / st) and cluster helpers.
 //
 // Every wait on an mbarrier is BOUNDED: after a time limit the waiter records a code in
