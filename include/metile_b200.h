@@ -17,7 +17,7 @@
  *   -6 null pointer, -7 workspace, -8 a bounded device-side wait gave up.
  * Errors are detected before any GPU work is queued.  There is no CPU fallback.
  *
- * `flags`: 0 selects the kernel by row count (CUDA-core GEMV for M <= 2, tcgen05 MMA above).
+ * `flags`: 0 selects the kernel by row count (CUDA-core GEMV for M = 1, tcgen05 MMA above).
  *   MT_FLAG_FORCE_GEMV (1)   CUDA-core GEMV (M <= 8)
  *   MT_FLAG_FORCE_UMMA (2)   tcgen05 path for any M (one accumulation order for every M:
  *                            use it when rows must be bit-identical across batch sizes 1..128)

@@ -11,8 +11,8 @@ Reference surface reproduced (names, argument order, defaults, error behaviour):
 
 Differences that are deliberate:
   * activations are bfloat16 torch CUDA tensors; packed weights keep the MLX layout unchanged;
-  * there is no timing tournament: the kernel is chosen by row count (CUDA-core GEMV for up to
-    two rows, tcgen05 MMA above), so `autotune`, `block`, `outputs_per_simdgroup` and
+  * there is no timing tournament: the kernel is chosen by row count (CUDA-core GEMV for one
+    row, tcgen05 MMA above), so `autotune`, `block`, `outputs_per_simdgroup` and
     `decode_dtype` are accepted for call-site compatibility and ignored;
   * any number of rows is served from one read of the weights (the reference's scalar kernels
     re-read them per row and its tuned residual path hands multi-row inputs to native MLX,
@@ -80,7 +80,7 @@ def _algorithm(rows, flags):
         return "gemv"
     if flags & (_lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A):
         return "umma_smem" if flags & _lib.FLAG_UMMA_SMEM_A else "umma"
-    return "gemv" if rows <= 2 else "umma"
+    return "gemv" if rows <= 1 else "umma"
 
 
 def _record(table, rows, input_features, output_features, dtype, group_size, bits, flags):

@@ -20,6 +20,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace mt {
 
@@ -50,13 +51,21 @@ struct GemvWeights {
     const uint16_t* biases;
 };
 
-// kM rows of activations; kRows output rows per half-warp per pass; kDual = gate|up with SwiGLU.
-template <int kM, int kRows, bool kDual>
+// kM rows of activations; kRows output rows per half-warp per pass; kDual = gate|up with SwiGLU;
+// kStageX = the activations are copied to shared memory once per CTA (else read from global).
+//
+// The (pass, slot) iteration space is flattened and software-pipelined: the packed words, scale and
+// bias of iteration i+1 are requested before iteration i is computed.  With programmatic dependent
+// launch the first request goes out before the kernel waits for its predecessor (nobody writes
+// weights); the activations -- the predecessor's output -- are read only after that wait, with
+// coherent loads.
+template <int kM, int kRows, bool kDual, bool kStageX>
 __global__ void __launch_bounds__(256)
-affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeights second,
-                   const uint16_t* __restrict__ residual, uint16_t* __restrict__ out, int K, int N, int ksplit) {
+affine_gemv_kernel(const uint16_t* x, GemvWeights first, GemvWeights second, const uint16_t* residual,
+                   uint16_t* __restrict__ out, int K, int N, int ksplit) {
     constexpr int kStreams = kDual ? 2 : 1;
     constexpr int kWarps = 8;
+    extern __shared__ uint4 x_shared[];  // kStageX: [kM][K/8] vectors of 8 bf16
     __shared__ float partial[kWarps][2][kStreams * kRows * kM];
     const int lane = threadIdx.x & 31;
     const int half = lane >> 4;
@@ -74,42 +83,62 @@ affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeight
     const int slot_end = min(slot_begin + slots_per_part, slots_per_row);
     const int team_global = blockIdx.x * teams_per_cta + team;
     const int teams_total = gridDim.x * teams_per_cta;
-    // Every warp of a CTA runs the same number of passes (the bound depends on blockIdx only),
+    // Every warp of a CTA runs the same number of iterations (the bounds depend on blockIdx only),
     // so the __syncthreads below are reached by all of them.
     const int passes = (N + teams_total * rows_per_pass - 1) / (teams_total * rows_per_pass);
+    const int steps = (slots_per_part + 15) >> 4;  // slot iterations per pass (some lanes idle in the last)
+    const int total = passes * steps;
 
-    for (int pass = 0; pass < passes; ++pass) {
+    struct Weights {
+        uint4 packed[kStreams][kRows];
+        uint32_t scale[kStreams][kRows], bias[kStreams][kRows];
+    };
+    auto request = [&](int index, Weights& w) {
+        const int pass = index / steps, step = index - pass * steps;
+        const int slot = slot_begin + l16 + (step << 4);
+        if (index >= total || slot >= slot_end) return;
         const int row_base = (pass * teams_total + team_global) * rows_per_pass;
-        float acc[kStreams][kRows][kM];
 #pragma unroll
-        for (int s = 0; s < kStreams; ++s)
+        for (int s = 0; s < kStreams; ++s) {
+            const GemvWeights& wt = s == 0 ? first : second;
 #pragma unroll
-            for (int r = 0; r < kRows; ++r)
-#pragma unroll
-                for (int m = 0; m < kM; ++m) acc[s][r][m] = 0.0f;
-
-        int rows[kRows];
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-            const int n = row_base + half * kRows + r;
-            rows[r] = n < N ? n : N - 1;  // clamp loads; the store is guarded
-        }
-
-        for (int slot = slot_begin + l16; slot < slot_end; slot += 16) {
-            uint4 packed[kStreams][kRows];
-            float scale[kStreams][kRows], bias[kStreams][kRows];
-#pragma unroll
-            for (int s = 0; s < kStreams; ++s) {
-                const GemvWeights& wt = s == 0 ? first : second;
-#pragma unroll
-                for (int r = 0; r < kRows; ++r) {
-                    packed[s][r] = ldg_stream_u4(
-                        reinterpret_cast<const uint4*>(wt.w + (size_t)rows[r] * words_per_row) + slot);
-                    const size_t g = (size_t)rows[r] * groups_per_row + (slot >> 1);
-                    scale[s][r] = bf16_bits_to_f32(__ldg(wt.scales + g));
-                    bias[s][r] = bf16_bits_to_f32(__ldg(wt.biases + g));
-                }
+            for (int r = 0; r < kRows; ++r) {
+                const int n = min(row_base + half * kRows + r, N - 1);  // clamp loads; the store is guarded
+                w.packed[s][r] = ldg_stream_u4(reinterpret_cast<const uint4*>(wt.w + (size_t)n * words_per_row) + slot);
+                const size_t g = (size_t)n * groups_per_row + (slot >> 1);
+                w.scale[s][r] = __ldg(wt.scales + g);
+                w.bias[s][r] = __ldg(wt.biases + g);
             }
+        }
+    };
+
+    ptx::griddep_launch_dependents();
+    Weights next;
+    request(0, next);
+    ptx::griddep_wait();  // activations and residual are the preceding kernel's output
+    if constexpr (kStageX) {
+        const int vectors = kM * (K >> 3);
+        for (int v = threadIdx.x; v < vectors; v += blockDim.x) x_shared[v] = ptx::ld_global_dependent_u4(x + (size_t)v * 8);
+        __syncthreads();
+    }
+
+    float acc[kStreams][kRows][kM];
+    for (int index = 0; index < total; ++index) {
+        const int pass = index / steps, step = index - pass * steps;
+        const int slot = slot_begin + l16 + (step << 4);
+        const int row_base = (pass * teams_total + team_global) * rows_per_pass;
+        if (step == 0) {
+#pragma unroll
+            for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+                for (int r = 0; r < kRows; ++r)
+#pragma unroll
+                    for (int m = 0; m < kM; ++m) acc[s][r][m] = 0.0f;
+        }
+        const Weights cur = next;
+        request(index + 1, next);
+
+        if (slot < slot_end) {
             float dot[kStreams][kRows][kM];
             float xsum[kM];
 #pragma unroll
@@ -125,8 +154,9 @@ affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeight
                 float xv[kM][8];
 #pragma unroll
                 for (int m = 0; m < kM; ++m) {
-                    const uint4 raw =
-                        __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)slot * 32 + wi * 8));
+                    uint4 raw;
+                    if constexpr (kStageX) raw = x_shared[m * (K >> 3) + slot * 4 + wi];
+                    else raw = ptx::ld_global_dependent_u4(x + (size_t)m * K + (size_t)slot * 32 + wi * 8);
                     xv[m][0] = bf16_lo(raw.x); xv[m][1] = bf16_hi(raw.x);
                     xv[m][2] = bf16_lo(raw.y); xv[m][3] = bf16_hi(raw.y);
                     xv[m][4] = bf16_lo(raw.z); xv[m][5] = bf16_hi(raw.z);
@@ -138,10 +168,10 @@ affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeight
                 for (int s = 0; s < kStreams; ++s)
 #pragma unroll
                     for (int r = 0; r < kRows; ++r) {
-                        const uint32_t word = wi == 0 ? packed[s][r].x
-                                            : wi == 1 ? packed[s][r].y
-                                            : wi == 2 ? packed[s][r].z
-                                                      : packed[s][r].w;
+                        const uint32_t word = wi == 0 ? cur.packed[s][r].x
+                                            : wi == 1 ? cur.packed[s][r].y
+                                            : wi == 2 ? cur.packed[s][r].z
+                                                      : cur.packed[s][r].w;
                         float q[8];
                         decode_nibbles_f32(word, q);
 #pragma unroll
@@ -153,13 +183,16 @@ affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeight
 #pragma unroll
             for (int s = 0; s < kStreams; ++s)
 #pragma unroll
-                for (int r = 0; r < kRows; ++r)
+                for (int r = 0; r < kRows; ++r) {
+                    const float scale = bf16_bits_to_f32(cur.scale[s][r]), bias = bf16_bits_to_f32(cur.bias[s][r]);
 #pragma unroll
                     for (int m = 0; m < kM; ++m)
-                        acc[s][r][m] = fmaf(scale[s][r], dot[s][r][m], fmaf(bias[s][r], xsum[m], acc[s][r][m]));
+                        acc[s][r][m] = fmaf(scale, dot[s][r][m], fmaf(bias, xsum[m], acc[s][r][m]));
+                }
         }
+        if (step != steps - 1) continue;
 
-        // 16-lane butterfly inside each half-warp; every lane ends with the full sum.
+        // ---- end of a pass: 16-lane butterfly inside each half-warp, then the K parts in order
 #pragma unroll
         for (int s = 0; s < kStreams; ++s)
 #pragma unroll
@@ -171,7 +204,6 @@ affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeight
                     for (int offset = 8; offset >= 1; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
                     acc[s][r][m] = v;
                 }
-
         if (ksplit > 1) {
             if (l16 == 0) {
 #pragma unroll
@@ -196,7 +228,6 @@ affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeight
             }
             __syncthreads();
         }
-
         if (part == 0 && l16 == 0) {
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
@@ -207,7 +238,7 @@ affine_gemv_kernel(const uint16_t* __restrict__ x, GemvWeights first, GemvWeight
                         float v;
                         if constexpr (kDual) v = swiglu_f32(acc[0][r][m], acc[kStreams - 1][r][m]);
                         else v = acc[0][r][m];
-                        if (residual) v += bf16_bits_to_f32(residual[(size_t)m * N + n]);
+                        if (residual) v += bf16_bits_to_f32(ptx::ld_global_dependent_u16(residual + (size_t)m * N + n));
                         out[(size_t)m * N + n] = f32_to_bf16_bits(v);
                     }
                 }
@@ -225,18 +256,50 @@ inline int gemv_ksplit(int K, int N) {
     return ksplit;
 }
 
-template <int kM, bool kDual>
-inline int launch_gemv_m(const uint16_t* x, GemvWeights a, GemvWeights b, const uint16_t* residual, uint16_t* out,
-                         int K, int N, int sm_count, cudaStream_t stream) {
+template <int kM, bool kDual, bool kStageX>
+inline int launch_gemv_instance(const uint16_t* x, GemvWeights a, GemvWeights b, const uint16_t* residual,
+                                uint16_t* out, int K, int N, int sm_count, cudaStream_t stream) {
     constexpr int kRows = kDual ? (kM <= 2 ? 2 : 1) : (kM <= 2 ? 4 : (kM <= 4 ? 2 : 1));
     constexpr int kWarps = 8;
+    auto kernel = affine_gemv_kernel<kM, kRows, kDual, kStageX>;
+    const int smem = kStageX ? kM * K * 2 : 0;
+    if (smem > 48 * 1024) {
+        static bool configured[64] = {};
+        int device = 0;
+        cudaGetDevice(&device);
+        if (device >= 64 || !configured[device]) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess)
+                return MT_ERR_LAUNCH;
+            if (device < 64) configured[device] = true;
+        }
+    }
     const int ksplit = gemv_ksplit(K, N);
     const int rows_per_cta = (kWarps / ksplit) * 2 * kRows;
     int grid = (N + rows_per_cta - 1) / rows_per_cta;
-    const int cap = sm_count * 16;
+    const int cap = sm_count * 2;  // two resident CTAs per SM; each loops over its share of the rows
     if (grid > cap) grid = cap;
-    affine_gemv_kernel<kM, kRows, kDual><<<grid, kWarps * 32, 0, stream>>>(x, a, b, residual, out, K, N, ksplit);
-    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid, 1, 1);
+    config.blockDim = dim3(kWarps * 32, 1, 1);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attrs;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, x, a, b, residual, out, K, N, ksplit) == cudaSuccess ? MT_OK
+                                                                                                     : MT_ERR_LAUNCH;
+}
+
+// Activations are staged in shared memory when they fit 96 KB (always for one or two rows at the
+// widths in use); larger batches read them from global memory.
+template <int kM, bool kDual>
+inline int launch_gemv_m(const uint16_t* x, GemvWeights a, GemvWeights b, const uint16_t* residual, uint16_t* out,
+                         int K, int N, int sm_count, cudaStream_t stream) {
+    if ((long)kM * K * 2 <= 96 * 1024)
+        return launch_gemv_instance<kM, kDual, true>(x, a, b, residual, out, K, N, sm_count, stream);
+    return launch_gemv_instance<kM, kDual, false>(x, a, b, residual, out, K, N, sm_count, stream);
 }
 
 template <bool kDual>

@@ -331,8 +331,8 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
             for (int q = 0; q < kXTasks; ++q) {
                 const int task = tid + q * kKBlockThreads;
                 if (task < x_tasks)
-                    xv_next[q] = ldg_nc_u4(x_base + (size_t)(task >> 3) * p.K + (size_t)kblock * kUmmaBlockK +
-                                           (task & 7) * 8);
+                    xv_next[q] = ptx::ld_global_dependent_u4(x_base + (size_t)(task >> 3) * p.K +
+                                                             (size_t)kblock * kUmmaBlockK + (task & 7) * 8);
             }
         };
         if (depth < nkb) {
@@ -503,7 +503,8 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
             }
             if (n < p.N) {
                 float v = kSwiglu ? swiglu_f32(first, second) : first;
-                if (!kSwiglu && p.residual) v += bf16_bits_to_f32(p.residual[(size_t)m * p.N + n]);
+                if (!kSwiglu && p.residual)
+                    v += bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.residual + (size_t)m * p.N + n));
                 p.out[(size_t)m * p.N + n] = f32_to_bf16_bits(v);
             }
         }

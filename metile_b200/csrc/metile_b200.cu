@@ -45,12 +45,13 @@ static int check_affine_ptrs(const void* x, const uint32_t* w, const void* s, co
     return MT_OK;
 }
 
-// Row-count split: the CUDA-core GEMV issues one FMA per weight per row, which stops hiding
-// behind HBM beyond two rows; from three rows on the tensor-core path is the faster one.
+// Row-count split: the CUDA-core GEMV issues one FMA per weight per row on top of the unpack, so
+// it is instruction-bound already at one row; measured, it wins at one row only (fused MLP at the
+// Llama-3.2-1B shape: 18.7 us vs 24.6 us) and loses from two rows on (26.1 us vs 24.7 us).
 static bool use_gemv(int M, unsigned int flags) {
     if (flags & MT_FLAG_FORCE_GEMV) return true;
     if (flags & (MT_FLAG_FORCE_UMMA | MT_FLAG_UMMA_SMEM_A)) return false;
-    return M <= 2;
+    return M <= 1;
 }
 
 static int run_projection(const void* x, const AffineWeights& first, const AffineWeights* second, const void* residual,

@@ -206,6 +206,20 @@ __device__ __forceinline__ void griddep_launch_dependents() {
 }
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Coherent 128-bit global load for data the PRECEDING kernel may still have been writing when this
+// kernel started (programmatic dependent launch): never the non-coherent (.nc / __ldg) path, and
+// volatile (volatile asm statements keep their order) so the compiler keeps it after griddep_wait().
+__device__ __forceinline__ uint4 ld_global_dependent_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_global_dependent_u16(const uint16_t* p) {
+    uint16_t v;
+    asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
 // ---- cluster -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

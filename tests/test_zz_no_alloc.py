@@ -44,7 +44,7 @@ def _run_pair(lib, device, rows, hidden, inter, seed):
     torch.cuda.synchronize()
     assert_bit_equal(out, reference, f"static vs workspace MLP, rows={rows}")
     oracle = A.mlp(f32(x), triple_np(gate), triple_np(up), triple_np(down), f32(res),
-                   weights="exact" if rows <= 2 else "bf16")
+                   weights="exact" if rows <= 1 else "bf16")
     assert_within(out, oracle, rel=4e-3, what=f"static MLP vs oracle, rows={rows}")
 
 
