@@ -487,25 +487,59 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
         constexpr int kParts = Cfg::kDequantWarps / 4;
         const int n = n0 + r;
         const uint32_t staging_addr = ptx::smem_u32(smem);
-        for (int m = rank + ksplit * part; m < p.M; m += ksplit * kParts) {
-            float first = 0.0f, second = 0.0f;
+        // Four rows per trip so that the remote loads of a trip are all in flight together; the
+        // partials of one output are still added in rank order.
+        constexpr int kUnroll = 4;
+        const int stride = ksplit * kParts;
+        for (int m0 = rank + ksplit * part; m0 < p.M; m0 += stride * kUnroll) {
+            float first[kUnroll], second[kUnroll], extra[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                first[u] = 0.0f;
+                second[u] = 0.0f;
+                extra[u] = 0.0f;
+            }
             if (ksplit > 1) {
                 for (int j = 0; j < ksplit; ++j) {
                     const uint32_t peer = ptx::map_to_cta(staging_addr, (uint32_t)j);
-                    first += ptx::ld_cluster_f32(peer + 4u * (uint32_t)(m * kUmmaTileRows + r));
-                    if constexpr (kSwiglu)
-                        second += ptx::ld_cluster_f32(peer + 4u * (uint32_t)((kMPad + m) * kUmmaTileRows + r));
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u) {
+                        const int m = m0 + u * stride;
+                        if (m < p.M) {
+                            first[u] += ptx::ld_cluster_f32(peer + 4u * (uint32_t)(m * kUmmaTileRows + r));
+                            if constexpr (kSwiglu)
+                                second[u] += ptx::ld_cluster_f32(peer + 4u * (uint32_t)((kMPad + m) * kUmmaTileRows + r));
+                        }
+                    }
                 }
             } else {
                 const float* staging = reinterpret_cast<const float*>(smem);
-                first = staging[m * kUmmaTileRows + r];
-                if constexpr (kSwiglu) second = staging[(kMPad + m) * kUmmaTileRows + r];
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const int m = m0 + u * stride;
+                    if (m < p.M) {
+                        first[u] = staging[m * kUmmaTileRows + r];
+                        if constexpr (kSwiglu) second[u] = staging[(kMPad + m) * kUmmaTileRows + r];
+                    }
+                }
             }
             if (n < p.N) {
-                float v = kSwiglu ? swiglu_f32(first, second) : first;
-                if (!kSwiglu && p.residual)
-                    v += bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.residual + (size_t)m * p.N + n));
-                p.out[(size_t)m * p.N + n] = f32_to_bf16_bits(v);
+                if (!kSwiglu && p.residual) {
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u) {
+                        const int m = m0 + u * stride;
+                        if (m < p.M)
+                            extra[u] = bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.residual + (size_t)m * p.N + n));
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const int m = m0 + u * stride;
+                    if (m < p.M) {
+                        const float v = kSwiglu ? swiglu_f32(first[u], second[u]) : first[u] + extra[u];
+                        p.out[(size_t)m * p.N + n] = f32_to_bf16_bits(v);
+                    }
+                }
             }
         }
     }

@@ -240,7 +240,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 }
 __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
     float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+    // volatile without a memory clobber: stays after the (volatile) cluster barrier, yet several of
+    // these can be in flight at once.
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr));
     return v;
 }
 
