@@ -23,6 +23,9 @@
  *                            use it when rows must be bit-identical across batch sizes 1..128)
  *   MT_FLAG_UMMA_SMEM_A (4)  tcgen05 path with the dequantised tile staged in shared memory
  *                            instead of tensor memory
+ *   MT_FLAG_UMMA_SCALED (8)  tcgen05 path for M <= 16 with exact weights: the tensor core sums
+ *                            x * (128 + q) per group and the group's scale and bias are applied to
+ *                            the partial sums in fp32
  *   MT_FLAG_GELU (16)        mt_dense_act: x/(1+exp(-1.702x)) instead of SiLU
  */
 #ifndef METILE_B200_H
@@ -38,6 +41,7 @@ extern "C" {
 #define MT_FLAG_FORCE_GEMV 0x1u
 #define MT_FLAG_FORCE_UMMA 0x2u
 #define MT_FLAG_UMMA_SMEM_A 0x4u
+#define MT_FLAG_UMMA_SCALED 0x8u
 #define MT_FLAG_GELU 0x10u
 
 /* Library version (major*10000 + minor*100 + patch). */

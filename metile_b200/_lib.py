@@ -15,6 +15,7 @@ LIBRARY_PATH = os.path.join(HERE, "csrc", "libmetile_b200.so")
 FLAG_FORCE_GEMV = 0x1
 FLAG_FORCE_UMMA = 0x2
 FLAG_UMMA_SMEM_A = 0x4
+FLAG_UMMA_SCALED = 0x8
 FLAG_GELU = 0x10
 
 _VALUE_ERRORS = {-1, -2, -3, -6, -7}

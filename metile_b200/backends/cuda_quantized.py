@@ -62,9 +62,11 @@ def batch_invariant(enabled=True):
 
 @contextlib.contextmanager
 def force_kernel(name):
-    """Pin the kernel family: "gemv", "umma" (A operand in tensor memory), "umma_smem" or None."""
+    """Pin the kernel family: "gemv", "umma" (A operand in tensor memory), "umma_smem",
+    "umma_scaled" (exact weights, up to 16 rows) or None."""
     table = {None: 0, "gemv": _lib.FLAG_FORCE_GEMV, "umma": _lib.FLAG_FORCE_UMMA,
-             "umma_smem": _lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A}
+             "umma_smem": _lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A,
+             "umma_scaled": _lib.FLAG_UMMA_SCALED}
     if name not in table:
         raise ValueError(f"unknown kernel family {name!r}")
     previous = _flags()
@@ -78,6 +80,8 @@ def force_kernel(name):
 def _algorithm(rows, flags):
     if flags & _lib.FLAG_FORCE_GEMV:
         return "gemv"
+    if flags & _lib.FLAG_UMMA_SCALED:
+        return "umma_scaled"
     if flags & (_lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A):
         return "umma_smem" if flags & _lib.FLAG_UMMA_SMEM_A else "umma"
     return "gemv" if rows <= 1 else "umma"

@@ -26,11 +26,12 @@ from tests.helpers import assert_bit_equal, assert_within, f32, triple_np
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kat.npz")
-FAMILIES = ("gemv", "umma", "umma_smem")
+FAMILIES = ("gemv", "umma", "umma_smem", "umma_scaled")
+MAX_ROWS = {"gemv": 8, "umma": 128, "umma_smem": 128, "umma_scaled": 16}
 
 
 def oracle_weights(family):
-    return "exact" if family == "gemv" else "bf16"
+    return "exact" if family in ("gemv", "umma_scaled") else "bf16"
 
 
 def bf16_tensor(bits, device):
@@ -61,8 +62,8 @@ def no_device_wait_gave_up(cuda_device):
 def test_golden_swiglu(cuda_device, family, name):
     kat = np.load(GOLDEN)
     x = bf16_tensor(kat[name + "_x"], cuda_device)
-    if family == "gemv" and x.shape[0] > 8:
-        pytest.skip("the CUDA-core GEMV serves up to 8 rows")
+    if x.shape[0] > MAX_ROWS[family]:
+        pytest.skip(f"the {family} family serves up to {MAX_ROWS[family]} rows")
     gate, up = golden_triple(kat, name + "_gate", cuda_device), golden_triple(kat, name + "_up", cuda_device)
     with B.force_kernel(family):
         y = B.mlx_affine_swiglu(x, *gate, *up)
@@ -140,7 +141,7 @@ SHAPES = [(64, 64), (256, 128), (512, 200), (1536, 1024), (2048, 512), (8192, 25
 @pytest.mark.parametrize("family", FAMILIES)
 @pytest.mark.parametrize("k,n", SHAPES)
 def test_projection_variants_against_oracle(cuda_device, family, k, n):
-    rows_list = (1, 2, 5, 8) if family == "gemv" else (1, 3, 16, 17, 64, 100, 128)
+    rows_list = {"gemv": (1, 2, 5, 8), "umma_scaled": (1, 3, 4, 7, 16)}.get(family, (1, 3, 16, 17, 64, 100, 128))
     gate, up = synth.affine_weight(10, n, k, cuda_device), synth.affine_weight(11, n, k, cuda_device)
     gate_np, up_np = triple_np(gate), triple_np(up)
     weights = oracle_weights(family)
@@ -223,15 +224,15 @@ def test_batch_invariance_bit_exact_1_to_128(cuda_device, k, n):
         assert_bit_equal(B.mlx_affine_swiglu(x[shuffled], *gate, *up), alone_swi[shuffled], "shuffled batch")
 
 
-@pytest.mark.parametrize("family", ["gemv", "umma_smem"])
+@pytest.mark.parametrize("family", ["gemv", "umma_smem", "umma_scaled"])
 def test_batch_invariance_within_each_family(cuda_device, family):
     k, n = 2048, 512
     gate, up = synth.affine_weight(10, n, k, cuda_device), synth.affine_weight(11, n, k, cuda_device)
-    top = 8 if family == "gemv" else 128
+    top = MAX_ROWS[family]
     x = synth.activations(99, top, k, cuda_device)
     with B.force_kernel(family):
         alone = torch.cat([B.mlx_affine_swiglu(x[i:i + 1], *gate, *up) for i in range(top)])
-        for rows in ((2, 3, 4, 8) if family == "gemv" else (16, 33, 128)):
+        for rows in {"gemv": (2, 3, 4, 8), "umma_scaled": (2, 5, 16)}.get(family, (16, 33, 128)):
             assert_bit_equal(B.mlx_affine_swiglu(x[:rows], *gate, *up), alone[:rows], f"{family} M={rows}")
 
 
