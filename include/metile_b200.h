@@ -27,6 +27,10 @@
  *                            x * (128 + q) per group and the group's scale and bias are applied to
  *                            the partial sums in fp32
  *   MT_FLAG_GELU (16)        mt_dense_act: x/(1+exp(-1.702x)) instead of SiLU
+ *   MT_FLAG_MLP_FUSED (32)   mt_affine_mlp: insist on the single-launch kernel (M <= 8, H and I
+ *                            multiples of 1024, the CTA's share of the weights must fit shared
+ *                            memory); -1 when it does not apply.  With flags = 0 mt_affine_mlp uses
+ *                            it for M <= 4 whenever it applies.
  */
 #ifndef METILE_B200_H
 #define METILE_B200_H
@@ -43,6 +47,7 @@ extern "C" {
 #define MT_FLAG_UMMA_SMEM_A 0x4u
 #define MT_FLAG_UMMA_SCALED 0x8u
 #define MT_FLAG_GELU 0x10u
+#define MT_FLAG_MLP_FUSED 0x20u
 
 /* Library version (major*10000 + minor*100 + patch). */
 int mt_version(void);

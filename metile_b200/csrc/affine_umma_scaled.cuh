@@ -55,13 +55,6 @@ struct UmmaScaledConfig {
     static_assert(kAbStages % kDepth == 0 && kUmmaKBlocksPerSlot % kDepth == 0, "depth groups");
 };
 
-// One packed word -> four bf16 pairs (128+q_i, 128+q_{i+4}), i = 0..3.
-__device__ __forceinline__ void unpack_word_offset128(uint32_t w, uint32_t* out) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(out[i]) : "r"(w >> (4 * i)), "r"(0x000F000Fu), "r"(0x43004300u));
-}
-
 template <int kT, bool kSwiglu>
 __global__ void __launch_bounds__(UmmaScaledConfig<kT>::kThreads, 1)
 affine_umma_scaled_kernel(const __grid_constant__ UmmaParams p) {

@@ -20,6 +20,8 @@
 #define MT_FLAG_FORCE_GEMV 0x1u   // CUDA-core GEMV regardless of row count (rows <= 8 only)
 #define MT_FLAG_FORCE_UMMA 0x2u   // tcgen05 path regardless of row count
 #define MT_FLAG_UMMA_SMEM_A 0x4u  // tcgen05 path with the dequantised tile staged in shared memory
+#define MT_FLAG_UMMA_SCALED 0x8u   // tcgen05 path, <= 16 rows, scale and bias applied to group partial sums
+#define MT_FLAG_MLP_FUSED 0x20u    // mt_affine_mlp: insist on the single-launch kernel (error if it does not apply)
 #define MT_FLAG_GELU 0x10u        // dense activation: x/(1+exp(-1.702x)) instead of SiLU
 
 namespace mt {
@@ -39,6 +41,15 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+}
+
+// One packed word (8 nibbles e0..e7) -> four bf16 pairs (128+e_i, 128+e_{i+4}), i = 0..3: the nibble
+// lands in the low mantissa bits of the bf16 value 128.0 (0x4300), so every value is exact.
+// (x & mask) | magic as ONE lop3 (truth table 0xEA) with both constants in registers.
+__device__ __forceinline__ void unpack_word_offset128(uint32_t w, uint32_t* out) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(out[i]) : "r"(w >> (4 * i)), "r"(0x000F000Fu), "r"(0x43004300u));
 }
 
 __device__ __forceinline__ float warp_sum_xor(float v) {

@@ -4,6 +4,7 @@
 
 #include "add_rmsnorm.cuh"
 #include "affine_gemv.cuh"
+#include "affine_mlp_fused.cuh"
 #include "affine_umma.cuh"
 #include "affine_umma_scaled.cuh"
 #include "common.cuh"
@@ -174,6 +175,11 @@ const char* mt_status_string(int status) {
 }
 
 // Diagnostic hook (not part of the public header): phase stamps of the tcgen05 kernel.
+int mt_debug_fused_pdl_state(void) {
+    int device = 0;
+    cudaGetDevice(&device);
+    return device < 64 ? g_fused_pdl_state[device] : 0;
+}
 void mt_debug_set_timeline(void* device_buffer) { g_timeline_buffer = static_cast<long long*>(device_buffer); }
 
 int mt_device_check(void) { return device_is_sm100() ? MT_OK : MT_ERR_DEVICE; }
@@ -238,6 +244,36 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
     if (M == 0) return MT_OK;
     if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < mt_affine_mlp_workspace_bytes(M, H, I))
         return MT_ERR_WORKSPACE;
+    // A handful of rows: the whole MLP as one cooperative launch when the shape fits it.  Any flag
+    // that pins a kernel family keeps the two-kernel path; MT_FLAG_MLP_FUSED insists on this one.
+    if (flags == 0 || (flags & MT_FLAG_MLP_FUSED)) {
+        if (!x || !gate_w || !gate_scales || !gate_biases || !up_w || !up_scales || !up_biases || !down_w ||
+            !down_scales || !down_biases || !out)
+            return MT_ERR_NULL;
+        if (!device_is_sm100()) return MT_ERR_DEVICE;
+        FusedMlpParams params;
+        params.x = static_cast<const uint16_t*>(x);
+        params.gate_w = gate_w;
+        params.up_w = up_w;
+        params.down_w = down_w;
+        params.gate_s = static_cast<const uint16_t*>(gate_scales);
+        params.gate_b = static_cast<const uint16_t*>(gate_biases);
+        params.up_s = static_cast<const uint16_t*>(up_scales);
+        params.up_b = static_cast<const uint16_t*>(up_biases);
+        params.down_s = static_cast<const uint16_t*>(down_scales);
+        params.down_b = static_cast<const uint16_t*>(down_biases);
+        params.residual = static_cast<const uint16_t*>(residual);
+        params.hidden = static_cast<uint16_t*>(workspace);
+        params.out = static_cast<uint16_t*>(out);
+        params.barrier = nullptr;
+        params.timeline = g_timeline_buffer;
+        params.M = M;
+        params.H = H;
+        params.I = I;
+        const int sms = device_sm_count();
+        if (fused_mlp_applicable(params, sms)) return launch_mlp_fused(params, sms, static_cast<cudaStream_t>(stream));
+        if (flags & MT_FLAG_MLP_FUSED) return MT_ERR_SHAPE;
+    }
     rc = mt_affine_swiglu(x, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, workspace, M, H, I,
                           group_size, bits, flags, stream);
     if (rc != MT_OK) return rc;

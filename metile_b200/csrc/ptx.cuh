@@ -91,6 +91,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// Bounded wait without a suspend-time hint: the waiter keeps polling, so it resumes within a few
+// cycles of the phase completing.  For waits on the critical path of a short pipeline stage.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               unsigned int code) {
+    for (int spin = 0; spin < 4096; ++spin)
+        if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long start = global_timer_ns();
+    while (true) {
+        for (int spin = 0; spin < 256; ++spin)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - start > kWaitLimitNs) {
+            if (atomicCAS(&g_device_status[0], 0u, code) == 0u) {
+                g_device_status[1] = blockIdx.x;
+                g_device_status[2] = threadIdx.x;
+                g_device_status[3] = parity;
+            }
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
 // ---- proxies / fences --------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -102,6 +125,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tensor_m
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_u32(smem_dst)), "l"(tensor_map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
         : "memory");
+}
+
+// ---- bulk copy: contiguous global bytes -> this CTA's shared memory, completion on an mbarrier.
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
 }
 
 __device__ __forceinline__ void prefetch_tensor_map(const void* tensor_map) {
@@ -228,6 +259,37 @@ __device__ __forceinline__ uint32_t ld_global_dependent_u16(const uint16_t* p) {
     uint16_t v;
     asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(p));
     return v;
+}
+
+// 128-bit load served from L2, for data other CTAs of the SAME grid wrote before a grid-wide barrier.
+__device__ __forceinline__ uint4 ld_global_l2_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long atom_add_release_gpu_u64(unsigned long long* p, unsigned long long v) {
+    unsigned long long old;
+    asm volatile("atom.add.release.gpu.global.u64 %0, [%1], %2;" : "=l"(old) : "l"(p), "l"(v) : "memory");
+    return old;
+}
+
+// ---- warp-level MMA: D[16x8] += A[16x16] * B[16x8], bf16 inputs, fp32 accumulate --------------
+// Fragments (g = lane / 4, t = lane % 4): a0 = A[g][2t, 2t+1], a1 = A[g+8][2t, 2t+1],
+// a2 = A[g][2t+8, 2t+9], a3 = A[g+8][2t+8, 2t+9]; b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g];
+// d0, d1 = D[g][2t, 2t+1], d2, d3 = D[g+8][2t, 2t+1].
+__device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                  uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // ---- cluster -----------------------------------------------------------------------------
