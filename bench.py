@@ -216,6 +216,7 @@ def log(message):
 def run_ours(args):
     import torch
 
+    from metile_b200 import _lib
     from metile_b200 import backends as B
     from metile_b200 import synth
     from metile_b200 import tp as tensor_parallel
@@ -371,39 +372,82 @@ def run_ours(args):
             "frac_of_roofline": max(hbm_seconds, tensor_seconds) / per_call,
         })
 
-    # ---- roofline of the dominant kernel: gate|up SwiGLU at M=1, timed alone ----------------------
+    # ---- roofline per kernel family, each timed alone; the headline one is the family with the largest
+    # share of the step (launches in a sweep x its duration) ------------------------------------------
     roofline = None
+    roofline_kernels = []
     if not tp:
-        gate_sets = [synth.mlp_weights(100, hidden, inter, device)[:2] for _ in range(copies)]
-        x1 = inputs[sweep[0]][0]
-        gate_cursor = [0]
+        library = _lib.load()
+        weight_sets = [synth.mlp_weights(100, hidden, inter, device) for _ in range(copies)]
+        cursor = [0]
 
-        def gate_up():
-            gate_cursor[0] = (gate_cursor[0] + 1) % copies
-            gate, up = gate_sets[gate_cursor[0]]
-            B.mlx_affine_swiglu(x1, *gate, *up)
+        def per_launch_seconds(fn, launches_per_call):
+            graph = capture(fn, 16)
+            graph.replay()
+            torch.cuda.synchronize()
+            return time_graph(graph, 10) / (160 * launches_per_call)
 
-        graph = capture(gate_up, 16)
-        graph.replay()
-        torch.cuda.synchronize()
-        per_launch = time_graph(graph, 10) / 160
-        algorithmic = 2 * hidden * inter * (0.5 + 4 / 64) + x1.numel() * 2 + inter * 2
-        achieved = algorithmic / per_launch / 1e9
-        roofline = {
-            "kernel": "gate|up SwiGLU projection, M=1 (" + B.mlx_affine_swiglu_dispatches()[0]["algorithm"] + ")",
-            "bound": "hbm",
-            "achieved": achieved,
-            "peak": hbm_peak,
-            "unit": "GB/s",
-            "frac": achieved / hbm_peak,
-            "peak_kind": f"of {peak_kind}",
-            # dram__bytes_read.sum + dram__bytes_write.sum of this kernel from the ncu capture summarised in
-            # profiles/affine_gemv_swiglu_m1_llama1b.md (equals the algorithmic bytes: no re-reads).
-            "traffic": 18904832,
-            "algorithmic_bytes_per_launch": int(algorithmic),
-            "us_per_launch": per_launch * 1e6,
-        }
-        del gate_sets
+        def entry(kernel, rows_served, seconds, algorithmic, traffic, profile):
+            achieved = algorithmic / seconds / 1e9
+            return {
+                "kernel": kernel,
+                "bound": "hbm",
+                "achieved": achieved,
+                "peak": hbm_peak,
+                "unit": "GB/s",
+                "frac": achieved / hbm_peak,
+                "peak_kind": f"of {peak_kind}",
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
+                # summarised in the named file under profiles/.
+                "traffic": traffic,
+                "traffic_source": profile,
+                "algorithmic_bytes_per_launch": int(algorithmic),
+                "us_per_launch": seconds * 1e6,
+                "launches_per_sweep": sum(1 for m in sweep if m in rows_served),
+            }
+
+        packed = hidden * inter * (0.5 + 4 / 64)  # one projection: nibbles + bf16 scales and biases
+        single_rows = [m for m in sweep if library.mt_affine_mlp_launches(m, hidden, inter, 0) == 1]
+        if single_rows:
+            x1, r1 = inputs[single_rows[0]]
+            executors_1 = [B.mlx_affine_mlp_executor(x1, *w[0], *w[1], *w[2], r1) for w in weight_sets]
+
+            def whole_mlp():
+                cursor[0] = (cursor[0] + 1) % copies
+                executors_1[cursor[0]](x1, r1)
+
+            seconds = per_launch_seconds(whole_mlp, 1)
+            roofline_kernels.append(entry(
+                "single-launch MLP, M=1 (affine_mlp_fused_kernel)", single_rows, seconds,
+                3 * packed + 2 * hidden * 2 + 2 * inter * 2 + hidden * 2, 28379392,
+                "profiles/affine_mlp_fused_m1_llama1b.md"))
+        two_kernel_rows = [m for m in sweep if m not in single_rows]
+        small = [m for m in two_kernel_rows if m <= 16]
+        if small:
+            m = small[-1]
+            xs = inputs[m][0]
+            hs = synth.activations(11, m, inter, device, std=0.3)
+            rs = inputs[m][1]
+
+            def gate_up():
+                cursor[0] = (cursor[0] + 1) % copies
+                gate, up, _ = weight_sets[cursor[0]]
+                B.mlx_affine_swiglu(xs, *gate, *up)
+
+            def down_projection():
+                cursor[0] = (cursor[0] + 1) % copies
+                B.mlx_affine_residual_qmv(hs, *weight_sets[cursor[0]][2], rs)
+
+            roofline_kernels.append(entry(
+                f"gate|up SwiGLU on tcgen05, 16-row instance at M={m} (affine_umma_kernel<2,16>)", small,
+                per_launch_seconds(gate_up, 1), 2 * packed + m * hidden * 2 + m * inter * 2, 18923520,
+                "profiles/affine_umma_swiglu_m1_llama1b.md"))
+            roofline_kernels.append(entry(
+                f"down projection on tcgen05, 16-row instance at M={m} (affine_umma_kernel<1,16>)", small,
+                per_launch_seconds(down_projection, 1), packed + m * inter * 2 + 2 * m * hidden * 2, None, None))
+        if roofline_kernels:
+            roofline = max(roofline_kernels, key=lambda e: e["launches_per_sweep"] * e["us_per_launch"])
+        del weight_sets
 
     log("per-M detail done")
     # ---- end to end through the public executor with host buffers ---------------------------------
@@ -443,7 +487,7 @@ def run_ours(args):
                                   "reference semantics; MLX-CPU is unavailable on this box"}
 
     if rank == 0:
-        kernels_per_mlp = 2
+        launches_per_sweep = sum(_lib.load().mt_affine_mlp_launches(m, hidden, inter, 0) for m in sweep)
         line = {
             "metric": "int4_fused_mlp_weight_GBps",
             "value": value,
@@ -464,10 +508,11 @@ def run_ours(args):
             "frac_of_hbm_peak": (local_bytes * len(sweep) / step_seconds / 1e9) / hbm_peak,
             "sweep": detail,
             "roofline": roofline,
+            "roofline_kernels": roofline_kernels,
             "cpu_baseline": cpu_baseline,
             "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_seconds * 1e3},
-            "gpu_launches": kernels_per_mlp * len(sweep) * args.steps,
+            "gpu_launches": launches_per_sweep * args.steps,
             "timing": "eager launches, CUDA events" if tp else "CUDA-graph replay, CUDA events",
             "clocks": clocks.summary(),
         }

@@ -1,40 +1,42 @@
 // The whole INT4 affine MLP  out = down(silu(x Wg^T) * (x Wu^T)) + residual  for a single
-// activation row as ONE cooperative launch that occupies HALF of every SM.
+// activation row as ONE cooperative launch, one CTA per SM.
 //
 // Why one launch.  At one row the MLP is a pure stream of packed weights (28 MB at the
 // Llama-3.2-1B shape: 4.4 us at the measured HBM rate), and two dependent kernels spend more time
 // starting, ramping up their loads and draining than moving those bytes.  Here a CTA streams its rows
-// of gate and up, then its rows of down, through ONE ring of shared-memory slots fed by bulk copies;
-// the two projections are separated by a grid-wide barrier (every hidden activation must exist
-// before any down row can be summed) and the copy engine keeps running across it, so the down rows
-// are already in the ring when the barrier opens.
-//
-// Why half an SM.  A CTA takes 544 threads, at most 56 registers per thread and under 113 KB of
-// shared memory, so the CTAs of TWO consecutive launches fit on an SM together.  With programmatic
-// dependent launch the next MLP's producer warp starts as soon as this one has started, fills its
-// ring (weights do not depend on the predecessor) and only its compute warps wait for this launch
-// to finish.  In a chain of launches HBM is therefore busy during each launch's barrier and tail.
+// of gate and up, then its rows of down, through ONE ring of shared-memory slots fed by bulk copies.
+// At the Llama-3.2-1B shape the ring holds the CTA's whole share (6 items of 36 KB), so every
+// weight byte of the MLP is requested in the first microsecond and HBM stays busy while the
+// arithmetic runs behind the copies; larger shapes reuse slots.  The two projections are separated
+// by a grid-wide barrier (every hidden activation must exist before any down row can be summed);
+// the down rows are already in the ring when the barrier opens.
 //
 // Work split.  CTA c owns gate/up rows [c*I/grid, (c+1)*I/grid) and down rows [c*H/grid,
 // (c+1)*H/grid).  A weight row of K columns is cut into K/1024 sets of 1024 columns (32 lanes x 32
-// nibbles): warp w of the 16 compute warps serves set w % sets and, in every ring item, the rows
-// w / sets + (16 / sets) * j.  Per-set partial sums of a row meet in shared memory and are added in
-// set order, so the fp32 order depends on (H, I, grid) only.
+// nibbles): warp w of the compute warps serves set w % sets and, in every ring item, the rows
+// w / sets + (warps / sets) * j.  Its activations (32 per lane, fp32 in registers) therefore never
+// change during a projection.  Per-set partial sums of a row meet in shared memory and are added
+// in set order, so the fp32 order depends on (H, I, grid) only.
 //
-// Arithmetic.  The activations sit in shared memory as fp32, transposed so that a lane reads the
-// four values it needs with one conflict-free 128-bit load.  A lane turns 16 bytes of a weight row
-// into the floats 128+q with one byte-permute each (the nibble becomes mantissa bits 16..19 of
-// 0x43000000 = 128.0f) and multiplies them with its 32 activations by plain FMAs, two weight rows
-// at a time.  Scale and bias are folded per lane:  s * dot + (b - 128 s) * (sum of the lane's
+// Arithmetic.  A lane turns 16 bytes of a weight row into the floats 128+q with one byte-permute
+// each (the nibble becomes mantissa bits 16..19 of 0x43000000 = 128.0f) and multiplies them with
+// its 32 activations by plain FMAs, four weight-row shares at a time so that their dependency
+// chains overlap.  Scale and bias are folded per lane:  s * dot + (b - 128 s) * (sum of the lane's
 // activations);  a butterfly adds the 32 lanes.  Weights are never rounded.
 //
-// Ring items (all the same size, 9*H bytes): gate|up item = 8 rows of gate, 8 rows of up and their
-// four 8-row blocks of scales and biases; down item = 16*H/I rows of down with their scales and
-// biases.
+// Ring items (all the same size): gate|up item = 16 rows of gate, 16 rows of up and their four
+// 16-row blocks of scales and biases (18*H bytes); down item = 32*H/I rows of down with their
+// scales and biases.
 //
-// Measured and dropped on B200: a warp-level MMA variant (mma.sync m16n8k16 issues about once per
-// 32 cycles per SM sub-partition, more than the FMAs cost) and the packed fma.rn.f32x2 (the
-// compiler moves every unpacked weight into a register pair first, two extra instructions per weight).
+// What bounds it (measured on B200).  One weight-row share costs about 76 instructions per warp
+// (32 byte-permutes, 32 FMAs, masks, scale fold, butterfly) and the SM sub-partition sustains about
+// 0.7 of them per cycle, so the MLP's 50 M weights take about 5 us of instruction issue per SM --
+// more than the 4.4 us the bytes take.  Eight compute warps with 146 registers beat sixteen with 96.
+// Also measured and dropped: a warp-level MMA variant (mma.sync m16n8k16 issues about once per 32
+// cycles per SM sub-partition), the packed fma.rn.f32x2 (the compiler moves every unpacked weight
+// into a register pair first, two extra instructions per weight), a bf16-pair unpack (same
+// instruction count as the byte-permutes), and a half-SM variant meant to let two launches overlap
+// (a cooperative launch does not start before its predecessor has drained, so nothing overlapped).
 #pragma once
 
 #include <cstdlib>
@@ -44,12 +46,18 @@
 
 namespace mt {
 
-constexpr int kFusedComputeWarps = 16;
+#ifndef MT_FUSED_WARPS
+#define MT_FUSED_WARPS 8
+#endif
+#ifndef MT_FUSED_ITEM_ROWS
+#define MT_FUSED_ITEM_ROWS 16
+#endif
+constexpr int kFusedComputeWarps = MT_FUSED_WARPS;
 constexpr int kFusedComputeThreads = kFusedComputeWarps * 32;
 constexpr int kFusedThreads = kFusedComputeThreads + 32;  // + the producer warp
 constexpr int kFusedMaxRows = 1;       // activation rows
 constexpr int kFusedMaxSlots = 12;
-constexpr int kFusedItemRows = 8;      // gate/up rows per ring item
+constexpr int kFusedItemRows = MT_FUSED_ITEM_ROWS;  // gate/up rows per ring item
 constexpr int kFusedSmemBudget = 226 * 1024;  // one CTA per SM
 constexpr int kFusedBarrierSlots = 64;
 
@@ -96,7 +104,7 @@ struct FusedMlpLayout {
     int sets1, sets2;          // 1024-column sets per weight row
     int item_bytes, slots;     // ring geometry
     int down_rows;             // down rows per ring item
-    int ring, acts, sums, scratch, bars, total;  // byte offsets
+    int ring, scratch, bars, total;  // byte offsets
 };
 
 __host__ __device__ inline int fused_round16(int v) { return (v + 15) & ~15; }
@@ -107,24 +115,19 @@ __host__ __device__ inline FusedMlpLayout fused_mlp_layout(int H, int I, int gri
     l.rows2_max = (H + grid - 1) / grid;
     l.sets1 = H / 1024;
     l.sets2 = I / 1024;
-    l.item_bytes = 9 * H;  // 8 rows x (H/2 gate + H/2 up) + 8 rows x 4 x H/32
-    int down = (16 * H) / I;  // rows r with r * (I/2 + 2 * I/32) <= 9 * H
-    if (down > 16) down = 16;
+    l.item_bytes = kFusedItemRows * (H + H / 8);  // rows x (H/2 gate + H/2 up) + rows x 4 x H/32
+    int down = (2 * kFusedItemRows * H) / I;      // rows r with r * (I/2 + 2 * I/32) <= item_bytes
+    if (down > 2 * kFusedItemRows) down = 2 * kFusedItemRows;
     l.down_rows = down;
-    const int widest = H > I ? H : I;
-    const int acts_bytes = widest * 4;         // fp32 activations of the wider projection
-    const int sums_bytes = (widest / 32) * 4;  // one sum per (set, lane)
     const int floats1 = l.rows1_max * 2 * l.sets1, floats2 = l.rows2_max * l.sets2;
     const int scratch_bytes = fused_round16(4 * (floats1 > floats2 ? floats1 : floats2));
     const int bars_bytes = 8 * (2 * kFusedMaxSlots) + 16;
-    const int fixed = acts_bytes + sums_bytes + scratch_bytes + bars_bytes + 128;
+    const int fixed = scratch_bytes + bars_bytes + 128;
     int slots = (kFusedSmemBudget - fixed) / l.item_bytes;
     if (slots > kFusedMaxSlots) slots = kFusedMaxSlots;
     l.slots = slots;
     l.ring = 0;
-    l.acts = l.ring + slots * l.item_bytes;
-    l.sums = l.acts + acts_bytes;
-    l.scratch = l.sums + sums_bytes;
+    l.scratch = l.ring + slots * l.item_bytes;
     l.bars = l.scratch + scratch_bytes;
     l.total = l.bars + bars_bytes;
     return l;
@@ -149,52 +152,62 @@ __device__ __forceinline__ void fused_compute_sync() {
     asm volatile("bar.sync 1, %0;" ::"r"(kFusedComputeThreads) : "memory");
 }
 
-// One activation row of `width` bf16 -> fp32 in shared memory, transposed for the compute warps:
-// the four floats k = 1024 s + 32 lane + 8 j + 4 h + (0..3) live at float4 index ((4 s + j) * 2 + h) * 32 + lane,
-// and sums[32 s + lane] is the sum of that lane's 32 values.  Called by all compute threads.
-template <bool kFromL2>
-__device__ __forceinline__ void stage_activations(const uint16_t* src, int width, float4* acts, float* sums) {
-    for (int c = threadIdx.x; c < (width >> 3); c += kFusedComputeThreads) {  // 16-byte chunk = 8 values
-        const uint4 v = kFromL2 ? ptx::ld_global_l2_u4(src + c * 8) : ptx::ld_global_dependent_u4(src + c * 8);
-        const int s = c >> 7, lane_of = (c >> 2) & 31, j = c & 3;
-        const float4 a = make_float4(bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
-        const float4 b = make_float4(bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w));
-        acts[((4 * s + j) * 2 + 0) * 32 + lane_of] = a;
-        acts[((4 * s + j) * 2 + 1) * 32 + lane_of] = b;
-        // Four consecutive threads hold the four words of one lane's 32 values.
-        float total = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
-        total += __shfl_xor_sync(0xFFFFFFFFu, total, 1);
-        total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
-        if (j == 0) sums[c >> 2] = total;
-    }
-}
+// The lane's 32 consecutive activations starting at column k0, as fp32 in registers, and their sum.
+struct LaneActivations {
+    float value[32];
+    float sum;
+};
 
-// Two weight-row shares (the 32 nibbles in pk0 and pk1, same columns) against the lane's activations.
-// Returns s * sum x (128+q) + (b - 128 s) * sum x for each, still to be added over the 32 lanes.
-__device__ __forceinline__ void fma_two_shares(const uint4& pk0, const uint4& pk1, uint32_t scale0, uint32_t bias0,
-                                               uint32_t scale1, uint32_t bias1, const float4* acts_of_set, int lane,
-                                               float lane_sum, float& out0, float& out1) {
-    const uint32_t w0[4] = {pk0.x, pk0.y, pk0.z, pk0.w};
-    const uint32_t w1[4] = {pk1.x, pk1.y, pk1.z, pk1.w};
-    float a0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, a1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+template <bool kFromL2>
+__device__ __forceinline__ void load_lane_activations(const uint16_t* src, int k0, LaneActivations& x) {
+    uint4 v[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float4 xa = acts_of_set[(j * 2 + 0) * 32 + lane];
-        const float4 xb = acts_of_set[(j * 2 + 1) * 32 + lane];
-        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-        float q0[8], q1[8];
-        unpack_word_f32_offset128(w0[j], q0);
-        unpack_word_f32_offset128(w1[j], q1);
+    for (int c = 0; c < 4; ++c) v[c] = kFromL2 ? ptx::ld_global_l2_u4(src + k0 + c * 8) : ptx::ld_global_dependent_u4(src + k0 + c * 8);
+    float total = 0.0f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            a0[e & 3] = fmaf(q0[e], xv[e], a0[e & 3]);
-            a1[e & 3] = fmaf(q1[e], xv[e], a1[e & 3]);
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t words[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x.value[8 * c + 2 * i] = bf16_lo(words[i]);
+            x.value[8 * c + 2 * i + 1] = bf16_hi(words[i]);
+            total += bf16_lo(words[i]);
+            total += bf16_hi(words[i]);
         }
     }
-    const float s0 = bf16_bits_to_f32(scale0), s1 = bf16_bits_to_f32(scale1);
-    const float o0 = fmaf(-128.0f, s0, bf16_bits_to_f32(bias0)), o1 = fmaf(-128.0f, s1, bf16_bits_to_f32(bias1));
-    out0 = fmaf(s0, (a0[0] + a0[1]) + (a0[2] + a0[3]), o0 * lane_sum);
-    out1 = fmaf(s1, (a1[0] + a1[1]) + (a1[2] + a1[3]), o1 * lane_sum);
+    x.sum = total;
+}
+
+// kN weight-row shares (32 nibbles each, same columns) against the lane's activations, interleaved so
+// that their dependency chains overlap.  out[i] = s_i * sum x (128+q_i) + (b_i - 128 s_i) * sum x,
+// added over the 32 lanes by a butterfly.
+template <int kN>
+__device__ __forceinline__ void fma_shares(const uint4 (&pk)[kN], const uint32_t (&scale_bits)[kN],
+                                           const uint32_t (&bias_bits)[kN], const LaneActivations& x, float (&out)[kN]) {
+    float a[kN][4];
+#pragma unroll
+    for (int i = 0; i < kN; ++i) a[i][0] = a[i][1] = a[i][2] = a[i][3] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int i = 0; i < kN; ++i) {
+            const uint32_t word = j == 0 ? pk[i].x : j == 1 ? pk[i].y : j == 2 ? pk[i].z : pk[i].w;
+            float q[8];
+            unpack_word_f32_offset128(word, q);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[i][e & 3] = fmaf(q[e], x.value[8 * j + e], a[i][e & 3]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kN; ++i) {
+        const float scale = bf16_bits_to_f32(scale_bits[i]);
+        const float offset = fmaf(-128.0f, scale, bf16_bits_to_f32(bias_bits[i]));
+        out[i] = fmaf(scale, (a[i][0] + a[i][1]) + (a[i][2] + a[i][3]), offset * x.sum);
+    }
+#pragma unroll
+    for (int offset = 16; offset >= 1; offset >>= 1)
+#pragma unroll
+        for (int i = 0; i < kN; ++i) out[i] += __shfl_xor_sync(0xFFFFFFFFu, out[i], offset);
 }
 
 // The grid-wide barrier, called by the compute warps: every CTA arrives once; the slot grows by
@@ -230,8 +243,6 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     const int H = p.H, I = p.I;
     const FusedMlpLayout lay = fused_mlp_layout(H, I, grid);
     uint8_t* ring = smem + lay.ring;
-    float4* acts = reinterpret_cast<float4*>(smem + lay.acts);
-    float* sums = reinterpret_cast<float*>(smem + lay.sums);
     float* scratch = reinterpret_cast<float*>(smem + lay.scratch);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + lay.bars);
     uint64_t* empty_bar = full_bar + kFusedMaxSlots;
@@ -267,9 +278,12 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
         // each issue one copy of an item.
         for (int it = 0; it < items1 + items2; ++it) {
             const int slot = it % slots, use = it / slots;
-            if (use > 0 && !ptx::mbar_wait_spin(&empty_bar[slot], (uint32_t)(use - 1) & 1u, abort_flag, kWaitFusedEmpty)) break;
+            if (use > 0 && !ptx::mbar_wait(&empty_bar[slot], (uint32_t)(use - 1) & 1u, abort_flag, kWaitFusedEmpty)) break;
             __syncwarp();
             uint8_t* dst = ring + (size_t)slot * lay.item_bytes;
+#ifdef MT_TIMELINE
+            if (p.timeline != nullptr && blockIdx.x == 0 && lane == 0 && it < 12) p.timeline[30 + it] = clock64();
+#endif
             if (it < items1) {
                 const int rows = min(kFusedItemRows, n1 - kFusedItemRows * it);
                 const size_t r0 = (size_t)(row1 + kFusedItemRows * it);
@@ -307,9 +321,6 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     float residual_value = 0.0f;  // fetched now, used at the very end
     if ((int)threadIdx.x < n2 && p.residual)
         residual_value = bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.residual + row2 + threadIdx.x));
-    stage_activations<false>(p.x, H, acts, sums);
-    fused_compute_sync();
-    MT_FUSED_STAMP(4);
     bool alive = true;
     {
         // ------------------------------------------------------------------ gate | up
@@ -317,40 +328,50 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
         const int set = warp % sets, first = warp / sets;
         const int chunk = (set * 32 + lane) * 16;        // byte offset of the lane's 32 nibbles in a row
         const int group = (set * 16 + (lane >> 1)) * 2;  // byte offset of their scale in a row of scales
-        const float4* acts_of_set = acts + set * 256;
-        const float lane_sum = sums[set * 32 + lane];
+        LaneActivations x;
+        load_lane_activations<false>(p.x, set * 1024 + lane * 32, x);
+        MT_FUSED_STAMP(4);
         for (int it = 0; it < items1 && alive; ++it) {
             const int slot = it % slots, use = it / slots;
-            if (!ptx::mbar_wait_spin(&full_bar[slot], (uint32_t)use & 1u, abort_flag, kWaitFusedFull)) { alive = false; break; }
+            if (!ptx::mbar_wait(&full_bar[slot], (uint32_t)use & 1u, abort_flag, kWaitFusedFull)) { alive = false; break; }
             __syncwarp();
             if (it < 4) MT_FUSED_STAMP(5 + it);
             const uint8_t* item = ring + (size_t)slot * lay.item_bytes;
             const uint8_t* tables = item + 2 * kFusedItemRows * rb1;
             const int rows_here = min(kFusedItemRows, n1 - kFusedItemRows * it);
-            for (int row = first; row < rows_here; row += step) {
-                const uint4 pk_gate = *reinterpret_cast<const uint4*>(item + row * rb1 + chunk);
-                const uint4 pk_up = *reinterpret_cast<const uint4*>(item + (kFusedItemRows + row) * rb1 + chunk);
-                const uint32_t gate_s = *reinterpret_cast<const uint16_t*>(tables + (0 * kFusedItemRows + row) * sb1 + group);
-                const uint32_t gate_b = *reinterpret_cast<const uint16_t*>(tables + (1 * kFusedItemRows + row) * sb1 + group);
-                const uint32_t up_s = *reinterpret_cast<const uint16_t*>(tables + (2 * kFusedItemRows + row) * sb1 + group);
-                const uint32_t up_b = *reinterpret_cast<const uint16_t*>(tables + (3 * kFusedItemRows + row) * sb1 + group);
-                float gate, up;
-                fma_two_shares(pk_gate, pk_up, gate_s, gate_b, up_s, up_b, acts_of_set, lane, lane_sum, gate, up);
+            // Two rows (gate and up of each: four shares) per step.
+            for (int base = first; base < rows_here; base += 2 * step) {
+                const bool pair = base + step < rows_here;
+                const int other = pair ? base + step : base;  // no second row: recompute the first, discard
+                uint4 pk[4];
+                uint32_t scale_bits[4], bias_bits[4];
 #pragma unroll
-                for (int offset = 16; offset >= 1; offset >>= 1) {
-                    gate += __shfl_xor_sync(0xFFFFFFFFu, gate, offset);
-                    up += __shfl_xor_sync(0xFFFFFFFFu, up, offset);
+                for (int i = 0; i < 4; ++i) {
+                    const int row = (i & 2) ? other : base, matrix = i & 1;
+                    pk[i] = *reinterpret_cast<const uint4*>(item + (matrix * kFusedItemRows + row) * rb1 + chunk);
+                    scale_bits[i] = *reinterpret_cast<const uint16_t*>(tables + ((2 * matrix) * kFusedItemRows + row) * sb1 + group);
+                    bias_bits[i] = *reinterpret_cast<const uint16_t*>(tables + ((2 * matrix + 1) * kFusedItemRows + row) * sb1 + group);
                 }
+                float part[4];
+                fma_shares<4>(pk, scale_bits, bias_bits, x, part);
                 if (lane == 0) {
-                    float* at = scratch + ((kFusedItemRows * it + row) * 2) * sets + set;
-                    at[0] = gate;
-                    at[sets] = up;
+                    float* at = scratch + ((kFusedItemRows * it + base) * 2) * sets + set;
+                    at[0] = part[0];
+                    at[sets] = part[1];
+                    if (pair) {
+                        at = scratch + ((kFusedItemRows * it + other) * 2) * sets + set;
+                        at[0] = part[2];
+                        at[sets] = part[3];
+                    }
                 }
             }
-            // The slot was read with ordinary loads and will be overwritten by the copy engine.
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
+            if (it < 8) MT_FUSED_STAMP(20 + it);
+            // The slot was read with ordinary loads; if the copy engine will overwrite it, order the two.
+            if (it + slots < items1 + items2) {
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
+            }
         }
         MT_FUSED_STAMP(9);
         fused_compute_sync();
@@ -367,50 +388,49 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     MT_FUSED_STAMP(11);
     fused_grid_barrier(p.barrier, grid, abort_flag);
     MT_FUSED_STAMP(12);
-    stage_activations<true>(p.hidden, I, acts, sums);
-    fused_compute_sync();
-    MT_FUSED_STAMP(13);
     {
         // ------------------------------------------------------------------ down
         const int sets = lay.sets2, step = kFusedComputeWarps / sets;
         const int set = warp % sets, first = warp / sets;
         const int chunk = (set * 32 + lane) * 16;
         const int group = (set * 16 + (lane >> 1)) * 2;
-        const float4* acts_of_set = acts + set * 256;
-        const float lane_sum = sums[set * 32 + lane];
+        LaneActivations x;
+        load_lane_activations<true>(p.hidden, set * 1024 + lane * 32, x);
+        MT_FUSED_STAMP(13);
         for (int j = 0; j < items2 && alive; ++j) {
             const int it = items1 + j;
             const int slot = it % slots, use = it / slots;
-            if (!ptx::mbar_wait_spin(&full_bar[slot], (uint32_t)use & 1u, abort_flag, kWaitFusedFull)) { alive = false; break; }
+            if (!ptx::mbar_wait(&full_bar[slot], (uint32_t)use & 1u, abort_flag, kWaitFusedFull)) { alive = false; break; }
             __syncwarp();
             if (j == 0) MT_FUSED_STAMP(14);
             const uint8_t* item = ring + (size_t)slot * lay.item_bytes;
             const uint8_t* tables = item + lay.down_rows * rb2;
             const int rows_here = min(lay.down_rows, n2 - lay.down_rows * j);
-            for (int base = first; base < rows_here; base += 2 * step) {
-                const bool pair = base + step < rows_here;
-                const int other = pair ? base + step : base;  // no second row: recompute the first, discard
-                const uint4 pk0 = *reinterpret_cast<const uint4*>(item + base * rb2 + chunk);
-                const uint4 pk1 = *reinterpret_cast<const uint4*>(item + other * rb2 + chunk);
-                const uint32_t s0 = *reinterpret_cast<const uint16_t*>(tables + base * sb2 + group);
-                const uint32_t b0 = *reinterpret_cast<const uint16_t*>(tables + (lay.down_rows + base) * sb2 + group);
-                const uint32_t s1 = *reinterpret_cast<const uint16_t*>(tables + other * sb2 + group);
-                const uint32_t b1 = *reinterpret_cast<const uint16_t*>(tables + (lay.down_rows + other) * sb2 + group);
-                float v0, v1;
-                fma_two_shares(pk0, pk1, s0, b0, s1, b1, acts_of_set, lane, lane_sum, v0, v1);
+            // Four rows per step.
+            for (int base = first; base < rows_here; base += 4 * step) {
+                uint4 pk[4];
+                uint32_t scale_bits[4], bias_bits[4];
+                int rows[4];
 #pragma unroll
-                for (int offset = 16; offset >= 1; offset >>= 1) {
-                    v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, offset);
-                    v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, offset);
+                for (int i = 0; i < 4; ++i) {
+                    rows[i] = base + i * step < rows_here ? base + i * step : base;  // past the end: recompute, discard
+                    pk[i] = *reinterpret_cast<const uint4*>(item + rows[i] * rb2 + chunk);
+                    scale_bits[i] = *reinterpret_cast<const uint16_t*>(tables + rows[i] * sb2 + group);
+                    bias_bits[i] = *reinterpret_cast<const uint16_t*>(tables + (lay.down_rows + rows[i]) * sb2 + group);
                 }
+                float part[4];
+                fma_shares<4>(pk, scale_bits, bias_bits, x, part);
                 if (lane == 0) {
-                    scratch[(lay.down_rows * j + base) * sets + set] = v0;
-                    if (pair) scratch[(lay.down_rows * j + other) * sets + set] = v1;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (base + i * step < rows_here) scratch[(lay.down_rows * j + rows[i]) * sets + set] = part[i];
                 }
             }
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
+            if (it + slots < items1 + items2) {
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
+            }
         }
         MT_FUSED_STAMP(15);
         fused_compute_sync();
@@ -427,7 +447,9 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
 // Whether the fused kernel serves this problem on a device with `sm_count` SMs.
 inline bool fused_mlp_applicable(const FusedMlpParams& p, int sm_count) {
     if (p.M != 1 || sm_count < 1) return false;
-    auto supported = [](int v) { return v == 1024 || v == 2048 || v == 4096 || v == 8192 || v == 16384; };  // sets divide 16
+    auto supported = [](int v) {  // a whole number of 1024-column sets that divides the compute warps
+        return v >= 1024 && v % 1024 == 0 && kFusedComputeWarps % (v / 1024) == 0;
+    };
     if (!supported(p.H) || !supported(p.I)) return false;
     const FusedMlpLayout lay = fused_mlp_layout(p.H, p.I, sm_count);
     if (lay.slots < 2 || lay.down_rows < 1) return false;

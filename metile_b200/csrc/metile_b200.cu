@@ -281,6 +281,17 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
                          stream);
 }
 
+int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags) {
+    if (M <= 0) return 0;
+    if (flags != 0 && !(flags & MT_FLAG_MLP_FUSED)) return 2;
+    FusedMlpParams params = {};
+    params.M = M;
+    params.H = H;
+    params.I = I;
+    const int sms = device_sm_count();
+    return sms > 0 && fused_mlp_applicable(params, sms) ? 1 : 2;  // null pointers count as aligned
+}
+
 size_t mt_affine_mlp_static_max_bytes(void) { return kStaticHiddenBytes; }
 
 int mt_affine_mlp_static(const void* x, const uint32_t* gate_w, const void* gate_scales, const void* gate_biases,
