@@ -18,7 +18,7 @@
  * Errors are detected before any GPU work is queued.  There is no CPU fallback.
  *
  * `flags`: 0 selects the kernel by row count (CUDA-core GEMV for M = 1, tcgen05 MMA above;
- * mt_affine_mlp with M = 1 runs as one launch when the shape allows, see MT_FLAG_MLP_FUSED).
+ * mt_affine_mlp with M <= 3 runs as one launch when the shape allows, see MT_FLAG_MLP_FUSED).
  *   MT_FLAG_FORCE_GEMV (1)   CUDA-core GEMV (M <= 8)
  *   MT_FLAG_FORCE_UMMA (2)   tcgen05 path for any M (one accumulation order for every M:
  *                            use it when rows must be bit-identical across batch sizes 1..128)
@@ -28,9 +28,9 @@
  *                            x * (128 + q) per group and the group's scale and bias are applied to
  *                            the partial sums in fp32
  *   MT_FLAG_GELU (16)        mt_dense_act: x/(1+exp(-1.702x)) instead of SiLU
- *   MT_FLAG_MLP_FUSED (32)   mt_affine_mlp: insist on the single-launch kernel (M = 1, H and I in
+ *   MT_FLAG_MLP_FUSED (32)   mt_affine_mlp: insist on the single-launch kernel (M <= 4, H and I in
  *                            {1024, 2048, 4096, 8192}); -1 when it does not apply.  With flags = 0
- *                            mt_affine_mlp uses it whenever it applies.
+ *                            mt_affine_mlp uses it for M <= 3 whenever it applies.
  */
 #ifndef METILE_B200_H
 #define METILE_B200_H
@@ -95,8 +95,8 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
                   unsigned int flags, void* stream);
 
 /* How many kernels mt_affine_mlp queues for this problem on the current device with 16-byte
- * aligned operands: 1 when the single-launch kernel serves it (one row, H and I a whole number of
- * 1024-column sets that divides the compute warps, ring fits shared memory), else 2 (gate|up
+ * aligned operands: 1 when the single-launch kernel serves it (up to three rows, or four with
+ * MT_FLAG_MLP_FUSED; H and I in {1024, 2048, 4096, 8192}), else 2 (gate|up
  * SwiGLU, then down); 0 for M <= 0.  No counterpart in the reference project; used for launch
  * accounting. */
 int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags);

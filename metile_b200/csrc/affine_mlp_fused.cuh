@@ -55,7 +55,9 @@ namespace mt {
 constexpr int kFusedComputeWarps = MT_FUSED_WARPS;
 constexpr int kFusedComputeThreads = kFusedComputeWarps * 32;
 constexpr int kFusedThreads = kFusedComputeThreads + 32;  // + the producer warp
-constexpr int kFusedMaxRows = 1;       // activation rows
+constexpr int kFusedMaxRows = 4;       // activation rows (each lane keeps 32 fp32 activations per row in registers)
+constexpr int kFusedDefaultRows = 3;   // rows served by default (measured faster than the two-kernel path up to
+                                       // three rows); four rows only when asked with MT_FLAG_MLP_FUSED
 constexpr int kFusedMaxSlots = 12;
 constexpr int kFusedItemRows = MT_FUSED_ITEM_ROWS;  // gate/up rows per ring item
 constexpr int kFusedSmemBudget = 226 * 1024;  // one CTA per SM
@@ -109,7 +111,7 @@ struct FusedMlpLayout {
 
 __host__ __device__ inline int fused_round16(int v) { return (v + 15) & ~15; }
 
-__host__ __device__ inline FusedMlpLayout fused_mlp_layout(int H, int I, int grid) {
+__host__ __device__ inline FusedMlpLayout fused_mlp_layout(int M, int H, int I, int grid) {
     FusedMlpLayout l;
     l.rows1_max = (I + grid - 1) / grid;
     l.rows2_max = (H + grid - 1) / grid;
@@ -119,7 +121,7 @@ __host__ __device__ inline FusedMlpLayout fused_mlp_layout(int H, int I, int gri
     int down = (2 * kFusedItemRows * H) / I;      // rows r with r * (I/2 + 2 * I/32) <= item_bytes
     if (down > 2 * kFusedItemRows) down = 2 * kFusedItemRows;
     l.down_rows = down;
-    const int floats1 = l.rows1_max * 2 * l.sets1, floats2 = l.rows2_max * l.sets2;
+    const int floats1 = l.rows1_max * 2 * l.sets1 * M, floats2 = l.rows2_max * l.sets2 * M;
     const int scratch_bytes = fused_round16(4 * (floats1 > floats2 ? floats1 : floats2));
     const int bars_bytes = 8 * (2 * kFusedMaxSlots) + 16;
     const int fixed = scratch_bytes + bars_bytes + 128;
@@ -152,41 +154,54 @@ __device__ __forceinline__ void fused_compute_sync() {
     asm volatile("bar.sync 1, %0;" ::"r"(kFusedComputeThreads) : "memory");
 }
 
-// The lane's 32 consecutive activations starting at column k0, as fp32 in registers, and their sum.
+// The lane's 32 consecutive activations starting at column k0 of each of kM rows, as fp32 in
+// registers, and their sums.
+template <int kM>
 struct LaneActivations {
-    float value[32];
-    float sum;
+    float value[kM][32];
+    float sum[kM];
 };
 
-template <bool kFromL2>
-__device__ __forceinline__ void load_lane_activations(const uint16_t* src, int k0, LaneActivations& x) {
-    uint4 v[4];
+template <int kM, bool kFromL2>
+__device__ __forceinline__ void load_lane_activations(const uint16_t* src, int width, int k0, LaneActivations<kM>& x) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) v[c] = kFromL2 ? ptx::ld_global_l2_u4(src + k0 + c * 8) : ptx::ld_global_dependent_u4(src + k0 + c * 8);
-    float total = 0.0f;
+    for (int m = 0; m < kM; ++m) {
+        const uint16_t* from = src + (size_t)m * width + k0;
+        uint4 v[4];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const uint32_t words[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+        for (int c = 0; c < 4; ++c) v[c] = kFromL2 ? ptx::ld_global_l2_u4(from + c * 8) : ptx::ld_global_dependent_u4(from + c * 8);
+        float total = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            x.value[8 * c + 2 * i] = bf16_lo(words[i]);
-            x.value[8 * c + 2 * i + 1] = bf16_hi(words[i]);
-            total += bf16_lo(words[i]);
-            total += bf16_hi(words[i]);
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t words[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                x.value[m][8 * c + 2 * i] = bf16_lo(words[i]);
+                x.value[m][8 * c + 2 * i + 1] = bf16_hi(words[i]);
+                total += bf16_lo(words[i]);
+                total += bf16_hi(words[i]);
+            }
         }
+        x.sum[m] = total;
     }
-    x.sum = total;
 }
 
 // kN weight-row shares (32 nibbles each, same columns) against the lane's activations, interleaved so
-// that their dependency chains overlap.  out[i] = s_i * sum x (128+q_i) + (b_i - 128 s_i) * sum x,
-// added over the 32 lanes by a butterfly.
-template <int kN>
+// that their dependency chains overlap.  out[i][m] = s_i * sum x_m (128+q_i) + (b_i - 128 s_i) * sum x_m,
+// added over the 32 lanes by a butterfly.  The unpacked weights are shared by the kM activation rows.
+template <int kN, int kM>
 __device__ __forceinline__ void fma_shares(const uint4 (&pk)[kN], const uint32_t (&scale_bits)[kN],
-                                           const uint32_t (&bias_bits)[kN], const LaneActivations& x, float (&out)[kN]) {
-    float a[kN][4];
+                                           const uint32_t (&bias_bits)[kN], const LaneActivations<kM>& x,
+                                           float (&out)[kN][kM]) {
+    constexpr int kChains = 4;  // independent accumulators per (share, row); the same for every kM, so a
+                                // row's fp32 order does not depend on how many rows share the launch
+    float a[kN][kM][kChains];
 #pragma unroll
-    for (int i = 0; i < kN; ++i) a[i][0] = a[i][1] = a[i][2] = a[i][3] = 0.0f;
+    for (int i = 0; i < kN; ++i)
+#pragma unroll
+        for (int m = 0; m < kM; ++m)
+#pragma unroll
+            for (int c = 0; c < kChains; ++c) a[i][m][c] = 0.0f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
 #pragma unroll
@@ -195,19 +210,28 @@ __device__ __forceinline__ void fma_shares(const uint4 (&pk)[kN], const uint32_t
             float q[8];
             unpack_word_f32_offset128(word, q);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) a[i][e & 3] = fmaf(q[e], x.value[8 * j + e], a[i][e & 3]);
+            for (int e = 0; e < 8; ++e)
+#pragma unroll
+                for (int m = 0; m < kM; ++m)
+                    a[i][m][e % kChains] = fmaf(q[e], x.value[m][8 * j + e], a[i][m][e % kChains]);
         }
     }
 #pragma unroll
     for (int i = 0; i < kN; ++i) {
         const float scale = bf16_bits_to_f32(scale_bits[i]);
         const float offset = fmaf(-128.0f, scale, bf16_bits_to_f32(bias_bits[i]));
-        out[i] = fmaf(scale, (a[i][0] + a[i][1]) + (a[i][2] + a[i][3]), offset * x.sum);
+#pragma unroll
+        for (int m = 0; m < kM; ++m) {
+            const float dot = (a[i][m][0] + a[i][m][1]) + (a[i][m][2] + a[i][m][3]);
+            out[i][m] = fmaf(scale, dot, offset * x.sum[m]);
+        }
     }
 #pragma unroll
     for (int offset = 16; offset >= 1; offset >>= 1)
 #pragma unroll
-        for (int i = 0; i < kN; ++i) out[i] += __shfl_xor_sync(0xFFFFFFFFu, out[i], offset);
+        for (int i = 0; i < kN; ++i)
+#pragma unroll
+            for (int m = 0; m < kM; ++m) out[i][m] += __shfl_xor_sync(0xFFFFFFFFu, out[i][m], offset);
 }
 
 // The grid-wide barrier, called by the compute warps: every CTA arrives once; the slot grows by
@@ -235,13 +259,15 @@ __device__ __forceinline__ void fused_grid_barrier(unsigned long long* slot, int
     fused_compute_sync();
 }
 
+template <int kM>
 __global__ void __launch_bounds__(kFusedThreads, 1)
 affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
+    constexpr int kShares = kM == 1 ? 4 : 2;  // weight-row shares in flight per warp
     extern __shared__ uint8_t fused_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fused_smem_raw) + 127) & ~(uintptr_t)127);
     const int grid = gridDim.x, cta = blockIdx.x;
     const int H = p.H, I = p.I;
-    const FusedMlpLayout lay = fused_mlp_layout(H, I, grid);
+    const FusedMlpLayout lay = fused_mlp_layout(kM, H, I, grid);
     uint8_t* ring = smem + lay.ring;
     float* scratch = reinterpret_cast<float*>(smem + lay.scratch);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + lay.bars);
@@ -319,17 +345,20 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     ptx::griddep_wait();  // the activations and the residual are the preceding kernel's output
     MT_FUSED_STAMP(3);
     float residual_value = 0.0f;  // fetched now, used at the very end
-    if ((int)threadIdx.x < n2 && p.residual)
-        residual_value = bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.residual + row2 + threadIdx.x));
+    if ((int)threadIdx.x < n2 * kM && p.residual) {
+        const int row = threadIdx.x / kM, m = threadIdx.x - row * kM;
+        residual_value = bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.residual + (size_t)m * H + row2 + row));
+    }
     bool alive = true;
     {
         // ------------------------------------------------------------------ gate | up
+        // A step of a warp = kShares of the item's 2 * rows share-rows (share-row 2 r + matrix).
         const int sets = lay.sets1, step = kFusedComputeWarps / sets;
         const int set = warp % sets, first = warp / sets;
         const int chunk = (set * 32 + lane) * 16;        // byte offset of the lane's 32 nibbles in a row
         const int group = (set * 16 + (lane >> 1)) * 2;  // byte offset of their scale in a row of scales
-        LaneActivations x;
-        load_lane_activations<false>(p.x, set * 1024 + lane * 32, x);
+        LaneActivations<kM> x;
+        load_lane_activations<kM, false>(p.x, H, set * 1024 + lane * 32, x);
         MT_FUSED_STAMP(4);
         for (int it = 0; it < items1 && alive; ++it) {
             const int slot = it % slots, use = it / slots;
@@ -338,31 +367,29 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
             if (it < 4) MT_FUSED_STAMP(5 + it);
             const uint8_t* item = ring + (size_t)slot * lay.item_bytes;
             const uint8_t* tables = item + 2 * kFusedItemRows * rb1;
-            const int rows_here = min(kFusedItemRows, n1 - kFusedItemRows * it);
-            // Two rows (gate and up of each: four shares) per step.
-            for (int base = first; base < rows_here; base += 2 * step) {
-                const bool pair = base + step < rows_here;
-                const int other = pair ? base + step : base;  // no second row: recompute the first, discard
-                uint4 pk[4];
-                uint32_t scale_bits[4], bias_bits[4];
+            const int share_rows = 2 * min(kFusedItemRows, n1 - kFusedItemRows * it);
+            for (int base = first; base < share_rows; base += kShares * step) {
+                uint4 pk[kShares];
+                uint32_t scale_bits[kShares], bias_bits[kShares];
+                int where[kShares];  // share-row, or the first one again past the end (computed, discarded)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int row = (i & 2) ? other : base, matrix = i & 1;
+                for (int i = 0; i < kShares; ++i) {
+                    where[i] = base + i * step < share_rows ? base + i * step : base;
+                    const int row = where[i] >> 1, matrix = where[i] & 1;
                     pk[i] = *reinterpret_cast<const uint4*>(item + (matrix * kFusedItemRows + row) * rb1 + chunk);
                     scale_bits[i] = *reinterpret_cast<const uint16_t*>(tables + ((2 * matrix) * kFusedItemRows + row) * sb1 + group);
                     bias_bits[i] = *reinterpret_cast<const uint16_t*>(tables + ((2 * matrix + 1) * kFusedItemRows + row) * sb1 + group);
                 }
-                float part[4];
-                fma_shares<4>(pk, scale_bits, bias_bits, x, part);
+                float part[kShares][kM];
+                fma_shares<kShares, kM>(pk, scale_bits, bias_bits, x, part);
                 if (lane == 0) {
-                    float* at = scratch + ((kFusedItemRows * it + base) * 2) * sets + set;
-                    at[0] = part[0];
-                    at[sets] = part[1];
-                    if (pair) {
-                        at = scratch + ((kFusedItemRows * it + other) * 2) * sets + set;
-                        at[0] = part[2];
-                        at[sets] = part[3];
-                    }
+#pragma unroll
+                    for (int i = 0; i < kShares; ++i)
+                        if (base + i * step < share_rows) {
+#pragma unroll
+                            for (int m = 0; m < kM; ++m)
+                                scratch[((2 * kFusedItemRows * it + where[i]) * sets + set) * kM + m] = part[i][m];
+                        }
                 }
             }
             if (it < 8) MT_FUSED_STAMP(20 + it);
@@ -376,13 +403,14 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
         MT_FUSED_STAMP(9);
         fused_compute_sync();
         MT_FUSED_STAMP(10);
-        for (int row = threadIdx.x; row < n1; row += kFusedComputeThreads) {
+        for (int idx = threadIdx.x; idx < n1 * kM; idx += kFusedComputeThreads) {
+            const int row = idx / kM, m = idx - row * kM;
             float gate = 0.0f, up = 0.0f;
             for (int s = 0; s < sets; ++s) {
-                gate += scratch[(row * 2 + 0) * sets + s];
-                up += scratch[(row * 2 + 1) * sets + s];
+                gate += scratch[((2 * row + 0) * sets + s) * kM + m];
+                up += scratch[((2 * row + 1) * sets + s) * kM + m];
             }
-            p.hidden[row1 + row] = f32_to_bf16_bits(swiglu_f32(gate, up));
+            p.hidden[(size_t)m * I + row1 + row] = f32_to_bf16_bits(swiglu_f32(gate, up));
         }
     }
     MT_FUSED_STAMP(11);
@@ -394,8 +422,8 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
         const int set = warp % sets, first = warp / sets;
         const int chunk = (set * 32 + lane) * 16;
         const int group = (set * 16 + (lane >> 1)) * 2;
-        LaneActivations x;
-        load_lane_activations<true>(p.hidden, set * 1024 + lane * 32, x);
+        LaneActivations<kM> x;
+        load_lane_activations<kM, true>(p.hidden, I, set * 1024 + lane * 32, x);
         MT_FUSED_STAMP(13);
         for (int j = 0; j < items2 && alive; ++j) {
             const int it = items1 + j;
@@ -406,24 +434,27 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
             const uint8_t* item = ring + (size_t)slot * lay.item_bytes;
             const uint8_t* tables = item + lay.down_rows * rb2;
             const int rows_here = min(lay.down_rows, n2 - lay.down_rows * j);
-            // Four rows per step.
-            for (int base = first; base < rows_here; base += 4 * step) {
-                uint4 pk[4];
-                uint32_t scale_bits[4], bias_bits[4];
-                int rows[4];
+            for (int base = first; base < rows_here; base += kShares * step) {
+                uint4 pk[kShares];
+                uint32_t scale_bits[kShares], bias_bits[kShares];
+                int rows[kShares];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < kShares; ++i) {
                     rows[i] = base + i * step < rows_here ? base + i * step : base;  // past the end: recompute, discard
                     pk[i] = *reinterpret_cast<const uint4*>(item + rows[i] * rb2 + chunk);
                     scale_bits[i] = *reinterpret_cast<const uint16_t*>(tables + rows[i] * sb2 + group);
                     bias_bits[i] = *reinterpret_cast<const uint16_t*>(tables + (lay.down_rows + rows[i]) * sb2 + group);
                 }
-                float part[4];
-                fma_shares<4>(pk, scale_bits, bias_bits, x, part);
+                float part[kShares][kM];
+                fma_shares<kShares, kM>(pk, scale_bits, bias_bits, x, part);
                 if (lane == 0) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (base + i * step < rows_here) scratch[(lay.down_rows * j + rows[i]) * sets + set] = part[i];
+                    for (int i = 0; i < kShares; ++i)
+                        if (base + i * step < rows_here) {
+#pragma unroll
+                            for (int m = 0; m < kM; ++m)
+                                scratch[((lay.down_rows * j + rows[i]) * sets + set) * kM + m] = part[i][m];
+                        }
                 }
             }
             if (it + slots < items1 + items2) {
@@ -434,11 +465,11 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
         }
         MT_FUSED_STAMP(15);
         fused_compute_sync();
-        if ((int)threadIdx.x < n2) {
-            const int row = threadIdx.x;
+        if ((int)threadIdx.x < n2 * kM) {
+            const int row = threadIdx.x / kM, m = threadIdx.x - row * kM;
             float v = 0.0f;
-            for (int s = 0; s < sets; ++s) v += scratch[row * sets + s];
-            p.out[row2 + row] = f32_to_bf16_bits(v + residual_value);
+            for (int s = 0; s < sets; ++s) v += scratch[(row * sets + s) * kM + m];
+            p.out[(size_t)m * H + row2 + row] = f32_to_bf16_bits(v + residual_value);
         }
     }
     MT_FUSED_STAMP(16);
@@ -446,14 +477,14 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
 
 // Whether the fused kernel serves this problem on a device with `sm_count` SMs.
 inline bool fused_mlp_applicable(const FusedMlpParams& p, int sm_count) {
-    if (p.M != 1 || sm_count < 1) return false;
+    if (p.M < 1 || p.M > kFusedMaxRows || sm_count < 1) return false;
     auto supported = [](int v) {  // a whole number of 1024-column sets that divides the compute warps
         return v >= 1024 && v % 1024 == 0 && kFusedComputeWarps % (v / 1024) == 0;
     };
     if (!supported(p.H) || !supported(p.I)) return false;
-    const FusedMlpLayout lay = fused_mlp_layout(p.H, p.I, sm_count);
+    const FusedMlpLayout lay = fused_mlp_layout(p.M, p.H, p.I, sm_count);
     if (lay.slots < 2 || lay.down_rows < 1) return false;
-    if (lay.rows2_max > kFusedComputeThreads) return false;
+    if (lay.rows2_max * p.M > kFusedComputeThreads) return false;
     if (lay.total + 128 > kFusedSmemBudget) return false;
     const void* pointers[] = {p.x, p.gate_w, p.up_w, p.down_w, p.gate_s, p.gate_b, p.up_s, p.up_b, p.down_s, p.down_b,
                               p.hidden};
@@ -465,21 +496,12 @@ inline bool fused_mlp_applicable(const FusedMlpParams& p, int sm_count) {
 // 0 = untried, 1 = programmatic dependent launch accepted together with a cooperative launch, -1 = refused.
 static int g_fused_pdl_state[64] = {};
 
-// Caller has checked fused_mlp_applicable().
-inline int launch_mlp_fused(FusedMlpParams params, int sm_count, cudaStream_t stream) {
-    static unsigned long long* slots[64] = {};
+template <int kM>
+inline int launch_mlp_fused_rows(const FusedMlpParams& params, int sm_count, int device, cudaStream_t stream) {
     static bool configured[64] = {};
-    static unsigned int launches = 0;
-    auto kernel = affine_mlp_fused_kernel;
-    int device = 0;
-    cudaGetDevice(&device);
-    if (device >= 64) return MT_ERR_DEVICE;
-    const int smem = fused_mlp_layout(params.H, params.I, sm_count).total + 128;
+    auto kernel = affine_mlp_fused_kernel<kM>;
+    const int smem = fused_mlp_layout(kM, params.H, params.I, sm_count).total + 128;
     if (!configured[device]) {
-        if (getenv("MT_FUSED_NO_PDL")) g_fused_pdl_state[device] = -1;  // diagnostic switch
-        void* address = nullptr;
-        if (cudaGetSymbolAddress(&address, g_fused_barrier) != cudaSuccess) return MT_ERR_LAUNCH;
-        slots[device] = static_cast<unsigned long long*>(address);
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBudget) != cudaSuccess)
             return MT_ERR_LAUNCH;
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -488,7 +510,6 @@ inline int launch_mlp_fused(FusedMlpParams params, int sm_count, cudaStream_t st
             return MT_ERR_LAUNCH;
         configured[device] = true;
     }
-    params.barrier = slots[device] + (__atomic_fetch_add(&launches, 1u, __ATOMIC_RELAXED) % kFusedBarrierSlots);
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(sm_count, 1, 1);
     config.blockDim = dim3(kFusedThreads, 1, 1);
@@ -515,6 +536,29 @@ inline int launch_mlp_fused(FusedMlpParams params, int sm_count, cudaStream_t st
     }
     config.numAttrs = g_fused_pdl_state[device] == 1 ? 2 : 1;
     return cudaLaunchKernelEx(&config, kernel, params) == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
+}
+
+// Caller has checked fused_mlp_applicable().
+inline int launch_mlp_fused(FusedMlpParams params, int sm_count, cudaStream_t stream) {
+    static unsigned long long* slots[64] = {};
+    static unsigned int launches = 0;
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 64) return MT_ERR_DEVICE;
+    if (!slots[device]) {
+        if (getenv("MT_FUSED_NO_PDL")) g_fused_pdl_state[device] = -1;  // diagnostic switch
+        void* address = nullptr;
+        if (cudaGetSymbolAddress(&address, g_fused_barrier) != cudaSuccess) return MT_ERR_LAUNCH;
+        slots[device] = static_cast<unsigned long long*>(address);
+    }
+    params.barrier = slots[device] + (__atomic_fetch_add(&launches, 1u, __ATOMIC_RELAXED) % kFusedBarrierSlots);
+    switch (params.M) {
+        case 1: return launch_mlp_fused_rows<1>(params, sm_count, device, stream);
+        case 2: return launch_mlp_fused_rows<2>(params, sm_count, device, stream);
+        case 3: return launch_mlp_fused_rows<3>(params, sm_count, device, stream);
+        case 4: return launch_mlp_fused_rows<4>(params, sm_count, device, stream);
+        default: return MT_ERR_SHAPE;
+    }
 }
 
 }  // namespace mt

@@ -271,7 +271,8 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
         params.H = H;
         params.I = I;
         const int sms = device_sm_count();
-        if (fused_mlp_applicable(params, sms)) return launch_mlp_fused(params, sms, static_cast<cudaStream_t>(stream));
+        if ((flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms))
+            return launch_mlp_fused(params, sms, static_cast<cudaStream_t>(stream));
         if (flags & MT_FLAG_MLP_FUSED) return MT_ERR_SHAPE;
     }
     rc = mt_affine_swiglu(x, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, workspace, M, H, I,
@@ -289,6 +290,7 @@ int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags) {
     params.H = H;
     params.I = I;
     const int sms = device_sm_count();
+    if (!flags && M > kFusedDefaultRows) return 2;
     return sms > 0 && fused_mlp_applicable(params, sms) ? 1 : 2;  // null pointers count as aligned
 }
 

@@ -206,45 +206,55 @@ def test_config1_fused_mlp_llama_1b(cuda_device, rows):
 
 
 @pytest.mark.parametrize("hidden,inter", [(2048, 8192), (1024, 2048), (1024, 1024), (2048, 4096), (4096, 2048)])
-def test_single_launch_mlp_for_one_row(cuda_device, hidden, inter):
-    """The single-launch MLP kernel (one activation row): exact weights, compared with the oracle at
-    the MLP tolerance; the default dispatch uses it, so both calls give the same bits; repeated
-    back-to-back launches (programmatic dependent launch between them) give the same bits too."""
+def test_single_launch_mlp_up_to_four_rows(cuda_device, hidden, inter):
+    """The single-launch MLP kernel (one to four activation rows): exact weights, compared with the
+    oracle at the MLP tolerance; a row's bits do not depend on how many rows share the launch; the
+    default dispatch uses it up to three rows; repeated back-to-back launches (programmatic
+    dependent launch between them) give the same bits."""
     gate, up, down = synth.mlp_weights(300, hidden, inter, cuda_device)
     triples_np = [triple_np(t) for t in (gate, up, down)]
-    x = synth.activations(5, 1, hidden, cuda_device)
-    res = synth.activations(6, 1, hidden, cuda_device)
+    x = synth.activations(5, 4, hidden, cuda_device)
+    res = synth.activations(6, 4, hidden, cuda_device)
     execute = B.mlx_affine_mlp_executor(x, *gate, *up, *down, res)
+    library = _lib.load()
     with B.force_kernel("mlp_fused"):
-        y = execute(x, res)
+        full = execute(x, res)
         again = [execute(x, res) for _ in range(4)]
-    assert_within(y, A.mlp(f32(x), *triples_np, f32(res)), rel=4e-3, what=f"single-launch MLP {hidden}x{inter}")
+        for rows in (1, 2, 3):
+            assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], f"{rows} rows alone vs in a batch of 4")
+        assert_bit_equal(execute(x[3:4], res[3:4]), full[3:4], "last row alone")
+    assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=4e-3, what=f"single-launch MLP {hidden}x{inter}")
     for other in again:
-        assert_bit_equal(other, y, "repeat launch")
-    assert_bit_equal(execute(x, res), y, "default dispatch is the single-launch kernel")
+        assert_bit_equal(other, full, "repeat launch")
+    for rows in (1, 2, 3):
+        assert library.mt_affine_mlp_launches(rows, hidden, inter, 0) == 1
+        assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], "default dispatch is the single-launch kernel")
+    assert library.mt_affine_mlp_launches(4, hidden, inter, 0) == 2
+    assert library.mt_affine_mlp_launches(4, hidden, inter, _lib.FLAG_MLP_FUSED) == 1
     # Without a residual, and against the two-kernel path (different fp32 order, same tolerance).
     no_residual = B.mlx_affine_mlp_executor(x, *gate, *up, *down, None)
     with B.force_kernel("mlp_fused"):
         y_plain = no_residual(x, None)
     assert_within(y_plain, A.mlp(f32(x), *triples_np, None), rel=4e-3, what="single-launch MLP, no residual")
-    with B.force_kernel("gemv"):
+    with B.force_kernel("umma"):
         y_two = execute(x, res)
-    assert_within(y, f32(y_two), rel=4e-3, what="single-launch vs two-kernel path")
+    assert_within(full, f32(y_two), rel=4e-3, what="single-launch vs two-kernel path")
 
 
 def test_single_launch_mlp_refuses_what_it_does_not_serve(cuda_device):
     gate, up, down = synth.mlp_weights(301, 2048, 8192, cuda_device)
-    x = synth.activations(5, 2, 2048, cuda_device)
+    x = synth.activations(5, 5, 2048, cuda_device)
     execute = B.mlx_affine_mlp_executor(x, *gate, *up, *down, x)
     with B.force_kernel("mlp_fused"):
         with pytest.raises(ValueError):
-            execute(x, x)  # two rows
+            execute(x, x)  # five rows
     gate, up, down = synth.mlp_weights(302, 1536, 1024, cuda_device)
     x = synth.activations(5, 1, 1536, cuda_device)
     execute = B.mlx_affine_mlp_executor(x, *gate, *up, *down, x)
     with B.force_kernel("mlp_fused"):
         with pytest.raises(ValueError):
-            execute(x, x)  # width that is not 1024 * 2^k
+            execute(x, x)  # width that is not a whole number of 1024-column sets
+    assert _lib.load().mt_affine_mlp_launches(1, 1536, 1024, 0) == 2
     assert_within(execute(x, x), A.mlp(f32(x), *[triple_np(t) for t in (gate, up, down)], f32(x)), rel=4e-3)
 
 
