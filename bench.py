@@ -450,15 +450,28 @@ def run_ours(args):
         del weight_sets
 
     log("per-M detail done")
-    # ---- end to end through the public executor with host buffers ---------------------------------
-    def e2e_step():
-        for m in sweep:
-            hx, hr = host_inputs[m]
-            x = hx.to(device, non_blocking=True)
-            r = hr.to(device, non_blocking=True)
-            y = next_executor()(x, r)
-            host_outputs[m].copy_(y, non_blocking=True)
-        torch.cuda.synchronize()
+    # ---- end to end with host buffers ---------------------------------------------------------------
+    # Single GPU: the C-ABI host entry point (mt_affine_mlp_host through mlx_affine_mlp_host_executor):
+    # one call queues the two host->device copies, the MLP and the device->host copy.  Tensor-parallel:
+    # the sharded executor on device tensors with the copies issued around it.
+    if tp:
+        def e2e_step():
+            for m in sweep:
+                hx, hr = host_inputs[m]
+                x = hx.to(device, non_blocking=True)
+                r = hr.to(device, non_blocking=True)
+                y = next_executor()(x, r)
+                host_outputs[m].copy_(y, non_blocking=True)
+            torch.cuda.synchronize()
+    else:
+        host_executors = [B.mlx_affine_mlp_host_executor(max(sweep), hidden, *e.weights) for e in executors]
+
+        def e2e_step():
+            for m in sweep:
+                hx, hr = host_inputs[m]
+                cursor[0] = (cursor[0] + 1) % copies
+                host_executors[cursor[0]](hx, hr, host_outputs[m])
+            torch.cuda.synchronize()
 
     log("e2e warm-up")
     for _ in range(3):

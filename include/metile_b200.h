@@ -94,6 +94,22 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
                   size_t workspace_bytes, void* out, int M, int H, int I, int group_size, int bits,
                   unsigned int flags, void* stream);
 
+/* mt_affine_mlp for activations that live in HOST memory: queues, in order on `stream`, the copy of
+ * x (and of residual, unless residual_host is NULL) from the host buffers into the caller's device
+ * staging buffers, mt_affine_mlp on those, and the copy of the result into out_host.  The host
+ * buffers should be page-locked (cudaHostAlloc / cudaHostRegister) so the copies are asynchronous;
+ * out_host is valid once the stream has been synchronised.  Staging buffers hold M*H bf16 each and
+ * `workspace` is as for mt_affine_mlp; nothing is allocated here.
+ * Replaces, for a host whose activations are not on the GPU, the same call sites as mt_affine_mlp;
+ * the reference has no such split because Apple GPUs share memory with the host. */
+int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_host, void* x_device,
+                       void* residual_device, void* out_device, const uint32_t* gate_w,
+                       const void* gate_scales, const void* gate_biases, const uint32_t* up_w,
+                       const void* up_scales, const void* up_biases, const uint32_t* down_w,
+                       const void* down_scales, const void* down_biases, void* workspace,
+                       size_t workspace_bytes, int M, int H, int I, int group_size, int bits,
+                       unsigned int flags, void* stream);
+
 /* How many kernels mt_affine_mlp queues for this problem on the current device with 16-byte
  * aligned operands: 1 when the single-launch kernel serves it (up to three rows, or four with
  * MT_FLAG_MLP_FUSED; H and I in {1024, 2048, 4096, 8192}), else 2 (gate|up

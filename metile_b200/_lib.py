@@ -36,6 +36,7 @@ SIGNATURES = {
     "mt_affine_swiglu": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _u, _p]),
     "mt_affine_mlp_workspace_bytes": (_z, [_i, _i, _i]),
     "mt_affine_mlp": (_i, [_p] * 12 + [_z, _p, _i, _i, _i, _i, _i, _u, _p]),
+    "mt_affine_mlp_host": (_i, [_p] * 16 + [_z, _i, _i, _i, _i, _i, _u, _p]),
     "mt_affine_mlp_launches": (_i, [_i, _i, _i, _u]),
     "mt_affine_mlp_static_max_bytes": (_z, []),
     "mt_affine_mlp_static": (_i, [_p] * 12 + [_i, _i, _i, _i, _i, _u, _p]),

@@ -10,6 +10,7 @@ from .cuda_quantized import (  # noqa: F401
     batch_invariant,
     force_kernel,
     mlx_affine_mlp_executor,
+    mlx_affine_mlp_host_executor,
     mlx_affine_qmv,
     mlx_affine_residual_qmv,
     mlx_affine_residual_qmv_dispatches,

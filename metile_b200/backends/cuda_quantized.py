@@ -23,6 +23,7 @@ Differences that are deliberate:
 from __future__ import annotations
 
 import contextlib
+import ctypes
 import threading
 
 import torch
@@ -250,6 +251,60 @@ def mlx_affine_mlp_executor(sample_values, gate_weight, gate_scales, gate_biases
     return execute
 
 
+def mlx_affine_mlp_host_executor(max_rows, hidden_features, gate_weight, gate_scales, gate_biases, up_weight,
+                                 up_scales, up_biases, down_weight, down_scales, down_biases, *,
+                                 group_size=64, bits=4):
+    """The fused MLP for activations that live in host memory.
+
+    Returns `execute(values, residual, out)` on page-locked CPU bfloat16 tensors of up to `max_rows`
+    rows: ONE C-ABI call (mt_affine_mlp_host) queues the host->device copies of the activations and
+    the residual, the MLP kernels and the device->host copy of the result on the current stream;
+    `out` is valid after `torch.cuda.current_stream().synchronize()`.  Device staging buffers and
+    the hidden workspace are allocated once, here.  No counterpart in the reference (unified
+    memory on Apple GPUs); the weights are the same MLX triples as for mlx_affine_mlp_executor.
+    """
+    name = "affine MLP (host buffers)"
+    device = gate_weight.device
+    probe = torch.empty((1, hidden_features), dtype=torch.bfloat16, device=device)
+    intermediate = check_affine_triple(name, probe, gate_weight, gate_scales, gate_biases, group_size, bits)
+    check_affine_triple(name, probe, up_weight, up_scales, up_biases, group_size, bits)
+    if gate_weight.shape != up_weight.shape:
+        raise ValueError("affine MLP requires matching gate/up weights")
+    probe_down = torch.empty((1, intermediate), dtype=torch.bfloat16, device=device)
+    if check_affine_triple(name, probe_down, down_weight, down_scales, down_biases, group_size,
+                           bits) != hidden_features:
+        raise ValueError("affine MLP down projection must map back to the input width")
+    lib = library()
+    bound = (gate_weight, gate_scales, gate_biases, up_weight, up_scales, up_biases, down_weight,
+             down_scales, down_biases)
+    pointers = [pointer(t) for t in bound]
+    staging = torch.empty((3, max_rows, hidden_features), dtype=torch.bfloat16, device=device)
+    workspace = torch.empty((max_rows, intermediate), dtype=torch.bfloat16, device=device)
+    stage_pointers = [ctypes.c_void_p(staging[i].data_ptr()) for i in range(3)]
+
+    def execute(values, residual, out):
+        for tensor in (values, residual, out):
+            if tensor is None:
+                continue
+            if tensor.is_cuda or tensor.dtype != torch.bfloat16 or not tensor.is_contiguous():
+                raise ValueError("host executor expects contiguous CPU bfloat16 tensors")
+            if tensor.shape[-1] != hidden_features or tensor.shape != values.shape:
+                raise ValueError("host executor received tensors of a different layout")
+        rows = values.numel() // hidden_features
+        if rows > max_rows:
+            raise ValueError(f"host executor was sized for {max_rows} rows, got {rows}")
+        code = lib.mt_affine_mlp_host(pointer(values), pointer(residual), pointer(out), stage_pointers[0],
+                                      stage_pointers[1], stage_pointers[2], *pointers, pointer(workspace),
+                                      workspace.numel() * 2, rows, hidden_features, intermediate, group_size,
+                                      bits, _flags(), stream_pointer(device))
+        _lib.check(code, name)
+        return out
+
+    execute.weights = bound
+    execute.buffers = (staging, workspace)
+    return execute
+
+
 def repack_mlx_affine_weight(weight, scales, biases):
     """MLX output-major layout -> the reference's K-major layout (two nibbles per byte, even flat
     index in the low nibble; scales and biases transposed).  Provided for callers that hold
@@ -297,6 +352,7 @@ def mlx_affine_residual_qmv_dispatches():
 __all__ = [
     "batch_invariant",
     "force_kernel",
+    "mlx_affine_mlp_host_executor",
     "mlx_affine_mlp_executor",
     "mlx_affine_qmv",
     "mlx_affine_residual_qmv",

@@ -282,6 +282,28 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
                          stream);
 }
 
+int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_host, void* x_device,
+                       void* residual_device, void* out_device, const uint32_t* gate_w, const void* gate_scales,
+                       const void* gate_biases, const uint32_t* up_w, const void* up_scales, const void* up_biases,
+                       const uint32_t* down_w, const void* down_scales, const void* down_biases, void* workspace,
+                       size_t workspace_bytes, int M, int H, int I, int group_size, int bits, unsigned int flags,
+                       void* stream) {
+    if (M < 0 || H < 1) return MT_ERR_SHAPE;
+    if (M == 0) return MT_OK;
+    if (!x_host || !out_host || !x_device || !out_device || (residual_host && !residual_device)) return MT_ERR_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t bytes = (size_t)M * (size_t)H * 2;
+    if (cudaMemcpyAsync(x_device, x_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return MT_ERR_LAUNCH;
+    if (residual_host &&
+        cudaMemcpyAsync(residual_device, residual_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+        return MT_ERR_LAUNCH;
+    const int rc = mt_affine_mlp(x_device, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, down_w,
+                                 down_scales, down_biases, residual_host ? residual_device : nullptr, workspace,
+                                 workspace_bytes, out_device, M, H, I, group_size, bits, flags, stream);
+    if (rc != MT_OK) return rc;
+    return cudaMemcpyAsync(out_host, out_device, bytes, cudaMemcpyDeviceToHost, s) == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
+}
+
 int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags) {
     if (M <= 0) return 0;
     if (flags != 0 && !(flags & MT_FLAG_MLP_FUSED)) return 2;

@@ -437,3 +437,27 @@ def test_errors_raise_and_nothing_falls_back(cuda_device):
             B.mlx_affine_qmv(synth.activations(2, 9, k, cuda_device), w, s, b)  # GEMV serves <= 8 rows
     empty = B.mlx_affine_qmv(x[:0], w, s, b)
     assert empty.shape == (0, n)
+
+
+def test_host_buffer_mlp_entry_point(cuda_device):
+    """mt_affine_mlp_host: activations, residual and result in page-locked host memory, one call."""
+    hidden, inter = 1024, 2048
+    gate, up, down = synth.mlp_weights(310, hidden, inter, cuda_device)
+    on_device = B.mlx_affine_mlp_executor(synth.activations(1, 1, hidden, cuda_device), *gate, *up, *down, None)
+    from_host = B.mlx_affine_mlp_host_executor(8, hidden, *gate, *up, *down)
+    for rows in (1, 3, 8):
+        x = synth.activations(20 + rows, rows, hidden, cuda_device)
+        res = synth.activations(30 + rows, rows, hidden, cuda_device)
+        hx, hr = x.cpu().pin_memory(), res.cpu().pin_memory()
+        out = torch.empty((rows, hidden), dtype=torch.bfloat16).pin_memory()
+        from_host(hx, hr, out)
+        torch.cuda.synchronize()
+        assert_bit_equal(out.to(cuda_device), on_device(x, res), f"host entry point, rows={rows}")
+        from_host(hx, None, out)
+        torch.cuda.synchronize()
+        assert_bit_equal(out.to(cuda_device), on_device(x, None), f"host entry point without residual, rows={rows}")
+    with pytest.raises(ValueError):
+        from_host(torch.empty((9, hidden), dtype=torch.bfloat16).pin_memory(), None,
+                  torch.empty((9, hidden), dtype=torch.bfloat16).pin_memory())
+    with pytest.raises(ValueError):
+        from_host(x, None, out)  # device tensor
