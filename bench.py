@@ -419,7 +419,7 @@ def run_ours(args):
             seconds = per_launch_seconds(whole_mlp, 1)
             roofline_kernels.append(entry(
                 "single-launch MLP, M=1 (affine_mlp_fused_kernel)", single_rows, seconds,
-                3 * packed + 2 * hidden * 2 + 2 * inter * 2 + hidden * 2, 28379392,
+                3 * packed + 2 * hidden * 2 + 2 * inter * 2 + hidden * 2, 28381952,
                 "profiles/affine_mlp_fused_m1_llama1b.md"))
         two_kernel_rows = [m for m in sweep if m not in single_rows]
         small = [m for m in two_kernel_rows if m <= 16]
@@ -440,7 +440,7 @@ def run_ours(args):
 
             roofline_kernels.append(entry(
                 f"gate|up SwiGLU on tcgen05, 16-row instance at M={m} (affine_umma_kernel<2,16>)", small,
-                per_launch_seconds(gate_up, 1), 2 * packed + m * hidden * 2 + m * inter * 2, 18923520,
+                per_launch_seconds(gate_up, 1), 2 * packed + m * hidden * 2 + m * inter * 2, 19020544,
                 "profiles/affine_umma_swiglu_m1_llama1b.md"))
             roofline_kernels.append(entry(
                 f"down projection on tcgen05, 16-row instance at M={m} (affine_umma_kernel<1,16>)", small,
@@ -534,13 +534,53 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_capture(spec):
+    """Six launches of one operator at the Llama-3.2-1B shape over six weight sets (170 MB, larger than
+    L2), nothing timed and nothing printed but a status line: the process profilers attach to."""
+    import torch
+
+    from metile_b200 import _lib
+    from metile_b200 import backends as B
+    from metile_b200 import synth
+
+    op, family, rows = spec.split(":")
+    rows = int(rows)
+    family = None if family == "default" else family
+    hidden, inter = 2048, 8192
+    device = torch.device("cuda:0")
+    sets = [synth.mlp_weights(200 + i, hidden, inter, device) for i in range(6)]
+    x = synth.activations(5, rows, hidden, device)
+    h = synth.activations(6, rows, inter, device, std=0.3)
+    r = synth.activations(7, rows, hidden, device)
+    executors = [B.mlx_affine_mlp_executor(x, *w[0], *w[1], *w[2], r) for w in sets]
+    with B.force_kernel(family):
+        for i, (gate, up, down) in enumerate(sets):
+            if op == "mlp":
+                executors[i](x, r)
+            elif op == "swiglu":
+                B.mlx_affine_swiglu(x, *gate, *up)
+            elif op == "down":
+                B.mlx_affine_residual_qmv(h, *down, r)
+            else:
+                raise SystemExit(f"unknown operator {op!r}")
+    torch.cuda.synchronize()
+    ok, words = _lib.device_status()
+    print(json.dumps({"capture": spec, "device_status_ok": bool(ok)}))
+    return 0 if ok else 1
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--capture", default=None, metavar="OP:FAMILY:ROWS",
+                        help="run a few launches of one operator and exit (a small target for ncu): OP is mlp, "
+                             "swiglu or down; FAMILY is default, mlp_fused, gemv, umma, umma_smem or umma_scaled")
     args = parser.parse_args()
+    if args.capture:
+        return run_capture(args.capture)
     if args.impl == "reference":
         if args.steps > 20:
             args.steps = 20  # each CPU step is a full sweep (~1 s); keep the run within minutes
@@ -552,4 +592,4 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    sys.exit(main())
