@@ -449,6 +449,32 @@ def run_ours(args):
             roofline = max(roofline_kernels, key=lambda e: e["launches_per_sweep"] * e["us_per_launch"])
         del weight_sets
 
+    # ---- tensor-parallel run: the SAME workload unsharded on one GPU (this rank's own), so that the
+    # strong-scaling ratio can be read from one line; eager launches and CUDA events like the headline.
+    one_gpu = None
+    if tp:
+        full_sets = [synth.mlp_weights(100, hidden, inter, device) for _ in range(2)]
+        sample = synth.activations(5, 1, hidden, device)
+        full_executors = [B.mlx_affine_mlp_executor(sample, *w[0], *w[1], *w[2], sample) for w in full_sets]
+        flip = [0]
+
+        def unsharded_sweep():
+            for m in sweep:
+                flip[0] ^= 1
+                full_executors[flip[0]](*inputs[m])
+
+        time_eager(unsharded_sweep, 3)
+        barrier()
+        one_seconds = time_eager(unsharded_sweep, args.steps) / args.steps
+        t = torch.tensor([one_seconds], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        one_seconds = float(t.item())
+        one_gpu = {"value": per_mlp_bytes * len(sweep) / one_seconds / 1e9, "unit": "GB/s",
+                   "ms_per_step": one_seconds * 1e3,
+                   "note": "same sweep, unsharded, one GPU (every rank runs it at once; slowest rank), "
+                           f"two weight sets of {per_mlp_bytes / 1e6:.0f} MB alternating"}
+        del full_executors, full_sets
+
     log("per-M detail done")
     # ---- end to end with host buffers ---------------------------------------------------------------
     # Single GPU: the C-ABI host entry point (mt_affine_mlp_host through mlx_affine_mlp_host_executor):
@@ -522,6 +548,7 @@ def run_ours(args):
             "sweep": detail,
             "roofline": roofline,
             "roofline_kernels": roofline_kernels,
+            "one_gpu_same_workload": one_gpu,
             "cpu_baseline": cpu_baseline,
             "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_seconds * 1e3},
