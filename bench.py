@@ -252,7 +252,14 @@ def run_ours(args):
             sample = synth.activations(5, 1, hidden, device)
             executors.append(B.mlx_affine_mlp_executor(sample, *gate, *up, *down, sample))
     inputs = {m: (synth.activations(5, m, hidden, device), synth.activations(6, m, hidden, device)) for m in sweep}
-    host_inputs = {m: (inputs[m][0].cpu().pin_memory(), inputs[m][1].cpu().pin_memory()) for m in sweep}
+    # Activations and residual of one call share a page-locked buffer, residual right after the
+    # activations, so that the host entry point can move both with one copy.
+    host_inputs = {}
+    for m in sweep:
+        both = torch.empty((2, m, hidden), dtype=torch.bfloat16).pin_memory()
+        both[0].copy_(inputs[m][0])
+        both[1].copy_(inputs[m][1])
+        host_inputs[m] = (both[0], both[1])
     host_outputs = {m: torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory() for m in sweep}
     cursor = [0]
 

@@ -99,7 +99,8 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
  * staging buffers, mt_affine_mlp on those, and the copy of the result into out_host.  The host
  * buffers should be page-locked (cudaHostAlloc / cudaHostRegister) so the copies are asynchronous;
  * out_host is valid once the stream has been synchronised.  Staging buffers hold M*H bf16 each and
- * `workspace` is as for mt_affine_mlp; nothing is allocated here.
+ * `workspace` is as for mt_affine_mlp; nothing is allocated here.  When residual_host directly follows
+ * x_host in memory and residual_device directly follows x_device, one copy moves both.
  * Replaces, for a host whose activations are not on the GPU, the same call sites as mt_affine_mlp;
  * the reference has no such split because Apple GPUs share memory with the host. */
 int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_host, void* x_device,

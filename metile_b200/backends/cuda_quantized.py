@@ -281,6 +281,7 @@ def mlx_affine_mlp_host_executor(max_rows, hidden_features, gate_weight, gate_sc
     staging = torch.empty((3, max_rows, hidden_features), dtype=torch.bfloat16, device=device)
     workspace = torch.empty((max_rows, intermediate), dtype=torch.bfloat16, device=device)
     stage_pointers = [ctypes.c_void_p(staging[i].data_ptr()) for i in range(3)]
+    row_bytes = hidden_features * 2
 
     def execute(values, residual, out):
         for tensor in (values, residual, out):
@@ -293,8 +294,12 @@ def mlx_affine_mlp_host_executor(max_rows, hidden_features, gate_weight, gate_sc
         rows = values.numel() // hidden_features
         if rows > max_rows:
             raise ValueError(f"host executor was sized for {max_rows} rows, got {rows}")
+        # The residual staging area starts right after the rows in use, so that a residual that
+        # follows the activations in host memory travels in the same copy.
+        residual_stage = ctypes.c_void_p(staging[0].data_ptr() + rows * row_bytes) if rows < max_rows \
+            else stage_pointers[1]
         code = lib.mt_affine_mlp_host(pointer(values), pointer(residual), pointer(out), stage_pointers[0],
-                                      stage_pointers[1], stage_pointers[2], *pointers, pointer(workspace),
+                                      residual_stage, stage_pointers[2], *pointers, pointer(workspace),
                                       workspace.numel() * 2, rows, hidden_features, intermediate, group_size,
                                       bits, _flags(), stream_pointer(device))
         _lib.check(code, name)

@@ -293,8 +293,14 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
     if (!x_host || !out_host || !x_device || !out_device || (residual_host && !residual_device)) return MT_ERR_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t bytes = (size_t)M * (size_t)H * 2;
-    if (cudaMemcpyAsync(x_device, x_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return MT_ERR_LAUNCH;
-    if (residual_host &&
+    // Small copies cost their fixed latency, not their bytes: when the residual follows the activations
+    // directly in host memory and the two staging buffers are adjacent as well, one copy moves both.
+    const bool adjacent = residual_host &&
+                          static_cast<const char*>(residual_host) == static_cast<const char*>(x_host) + bytes &&
+                          static_cast<char*>(residual_device) == static_cast<char*>(x_device) + bytes;
+    if (cudaMemcpyAsync(x_device, x_host, adjacent ? 2 * bytes : bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+        return MT_ERR_LAUNCH;
+    if (residual_host && !adjacent &&
         cudaMemcpyAsync(residual_device, residual_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
         return MT_ERR_LAUNCH;
     const int rc = mt_affine_mlp(x_device, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, down_w,
