@@ -30,7 +30,8 @@
  *   MT_FLAG_GELU (16)        mt_dense_act: x/(1+exp(-1.702x)) instead of SiLU
  *   MT_FLAG_MLP_FUSED (32)   mt_affine_mlp: insist on the single-launch kernel (M <= 4, H and I in
  *                            {1024, 2048, 4096, 8192}); -1 when it does not apply.  With flags = 0
- *                            mt_affine_mlp uses it for M <= 3 whenever it applies.
+ *                            mt_affine_mlp uses it for M <= 3 whenever it applies, and takes the
+ *                            two-kernel path if the driver refuses the cooperative launch.
  */
 #ifndef METILE_B200_H
 #define METILE_B200_H
@@ -48,6 +49,7 @@ extern "C" {
 #define MT_FLAG_UMMA_SCALED 0x8u
 #define MT_FLAG_GELU 0x10u
 #define MT_FLAG_MLP_FUSED 0x20u
+#define MT_FLAG_HOST_PAIR 0x40u
 
 /* Library version (major*10000 + minor*100 + patch). */
 int mt_version(void);
@@ -99,8 +101,10 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
  * staging buffers, mt_affine_mlp on those, and the copy of the result into out_host.  The host
  * buffers should be page-locked (cudaHostAlloc / cudaHostRegister) so the copies are asynchronous;
  * out_host is valid once the stream has been synchronised.  Staging buffers hold M*H bf16 each and
- * `workspace` is as for mt_affine_mlp; nothing is allocated here.  When residual_host directly follows
- * x_host in memory and residual_device directly follows x_device, one copy moves both.
+ * `workspace` is as for mt_affine_mlp; nothing is allocated here.  With MT_FLAG_HOST_PAIR the caller
+ * states that residual_host directly follows x_host inside ONE host allocation; if residual_device
+ * also directly follows x_device, one copy moves both (small copies cost their latency, not their
+ * bytes).  The flag has no other effect.
  * Replaces, for a host whose activations are not on the GPU, the same call sites as mt_affine_mlp;
  * the reference has no such split because Apple GPUs share memory with the host. */
 int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_host, void* x_device,

@@ -298,10 +298,14 @@ def mlx_affine_mlp_host_executor(max_rows, hidden_features, gate_weight, gate_sc
         # follows the activations in host memory travels in the same copy.
         residual_stage = ctypes.c_void_p(staging[0].data_ptr() + rows * row_bytes) if rows < max_rows \
             else stage_pointers[1]
+        flags = _flags()
+        if (residual is not None and residual.data_ptr() == values.data_ptr() + rows * row_bytes
+                and residual.untyped_storage().data_ptr() == values.untyped_storage().data_ptr()):
+            flags |= _lib.FLAG_HOST_PAIR  # two views of one page-locked buffer: one copy moves both
         code = lib.mt_affine_mlp_host(pointer(values), pointer(residual), pointer(out), stage_pointers[0],
                                       residual_stage, stage_pointers[2], *pointers, pointer(workspace),
                                       workspace.numel() * 2, rows, hidden_features, intermediate, group_size,
-                                      bits, _flags(), stream_pointer(device))
+                                      bits, flags, stream_pointer(device))
         _lib.check(code, name)
         return out
 

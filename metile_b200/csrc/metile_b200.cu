@@ -271,8 +271,14 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
         params.H = H;
         params.I = I;
         const int sms = device_sm_count();
-        if ((flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms))
-            return launch_mlp_fused(params, sms, static_cast<cudaStream_t>(stream));
+        if ((flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms)) {
+            const int fused_rc = launch_mlp_fused(params, sms, static_cast<cudaStream_t>(stream));
+            // A cooperative launch is refused when the whole grid cannot be resident (a GPU shared with
+            // another context, a carve-out that leaves too little shared memory).  Nothing was queued:
+            // the default dispatch then takes the two-kernel path; an explicit request reports it.
+            if (fused_rc != MT_ERR_LAUNCH || (flags & MT_FLAG_MLP_FUSED)) return fused_rc;
+            cudaGetLastError();
+        }
         if (flags & MT_FLAG_MLP_FUSED) return MT_ERR_SHAPE;
     }
     rc = mt_affine_swiglu(x, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, workspace, M, H, I,
@@ -295,7 +301,8 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
     const size_t bytes = (size_t)M * (size_t)H * 2;
     // Small copies cost their fixed latency, not their bytes: when the residual follows the activations
     // directly in host memory and the two staging buffers are adjacent as well, one copy moves both.
-    const bool adjacent = residual_host &&
+    // The caller vouches with MT_FLAG_HOST_PAIR that both lie in ONE host allocation (a copy may not span two).
+    const bool adjacent = residual_host && (flags & MT_FLAG_HOST_PAIR) &&
                           static_cast<const char*>(residual_host) == static_cast<const char*>(x_host) + bytes &&
                           static_cast<char*>(residual_device) == static_cast<char*>(x_device) + bytes;
     if (cudaMemcpyAsync(x_device, x_host, adjacent ? 2 * bytes : bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
@@ -305,7 +312,8 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
         return MT_ERR_LAUNCH;
     const int rc = mt_affine_mlp(x_device, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, down_w,
                                  down_scales, down_biases, residual_host ? residual_device : nullptr, workspace,
-                                 workspace_bytes, out_device, M, H, I, group_size, bits, flags, stream);
+                                 workspace_bytes, out_device, M, H, I, group_size, bits, flags & ~MT_FLAG_HOST_PAIR,
+                                 stream);
     if (rc != MT_OK) return rc;
     return cudaMemcpyAsync(out_host, out_device, bytes, cudaMemcpyDeviceToHost, s) == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
 }

@@ -456,6 +456,13 @@ def test_host_buffer_mlp_entry_point(cuda_device):
         from_host(hx, None, out)
         torch.cuda.synchronize()
         assert_bit_equal(out.to(cuda_device), on_device(x, None), f"host entry point without residual, rows={rows}")
+    # Activations and residual as two views of one page-locked buffer travel in one copy.
+    both = torch.empty((2, rows, hidden), dtype=torch.bfloat16).pin_memory()
+    both[0].copy_(x)
+    both[1].copy_(res)
+    from_host(both[0], both[1], out)
+    torch.cuda.synchronize()
+    assert_bit_equal(out.to(cuda_device), on_device(x, res), "host entry point, paired buffer")
     with pytest.raises(ValueError):
         from_host(torch.empty((9, hidden), dtype=torch.bfloat16).pin_memory(), None,
                   torch.empty((9, hidden), dtype=torch.bfloat16).pin_memory())
