@@ -32,6 +32,10 @@
  *                            {1024, 2048, 4096, 8192}); -1 when it does not apply.  With flags = 0
  *                            mt_affine_mlp uses it for M <= 3 whenever it applies, and takes the
  *                            two-kernel path if the driver refuses the cooperative launch.
+ *   MT_FLAG_MLP_FUSED_MMA (128) mt_affine_mlp: insist on the warp-MMA variant of the single-launch
+ *                            kernel (M <= 8, H in {512, 1024, 1536, 2048}, I a multiple of 512); -1
+ *                            when it does not apply.  Opt-in only: measured no faster than the
+ *                            two-kernel tensor-core path.
  */
 #ifndef METILE_B200_H
 #define METILE_B200_H
@@ -50,6 +54,7 @@ extern "C" {
 #define MT_FLAG_GELU 0x10u
 #define MT_FLAG_MLP_FUSED 0x20u
 #define MT_FLAG_HOST_PAIR 0x40u
+#define MT_FLAG_MLP_FUSED_MMA 0x80u
 
 /* Library version (major*10000 + minor*100 + patch). */
 int mt_version(void);
@@ -116,8 +121,9 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
                        unsigned int flags, void* stream);
 
 /* How many kernels mt_affine_mlp queues for this problem on the current device with 16-byte
- * aligned operands: 1 when the single-launch kernel serves it (up to three rows, or four with
- * MT_FLAG_MLP_FUSED; H and I in {1024, 2048, 4096, 8192}), else 2 (gate|up
+ * aligned operands: 1 when a single-launch kernel serves it (up to three rows on CUDA cores, four with
+ * MT_FLAG_MLP_FUSED, H and I in {1024, 2048, 4096, 8192}; up to eight rows on mma.sync with
+ * MT_FLAG_MLP_FUSED_MMA, H <= 2048), else 2 (gate|up
  * SwiGLU, then down); 0 for M <= 0.  No counterpart in the reference project; used for launch
  * accounting. */
 int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags);

@@ -18,6 +18,7 @@ FLAG_UMMA_SMEM_A = 0x4
 FLAG_UMMA_SCALED = 0x8
 FLAG_MLP_FUSED = 0x20
 FLAG_HOST_PAIR = 0x40
+FLAG_MLP_FUSED_MMA = 0x80
 FLAG_GELU = 0x10
 
 _VALUE_ERRORS = {-1, -2, -3, -6, -7}

@@ -64,11 +64,12 @@ def batch_invariant(enabled=True):
 @contextlib.contextmanager
 def force_kernel(name):
     """Pin the kernel family: "gemv", "umma" (A operand in tensor memory), "umma_smem",
-    "umma_scaled" (exact weights, up to 16 rows), "mlp_fused" (the single-launch MLP; projections
-    called on their own are unaffected) or None."""
+    "umma_scaled" (exact weights, up to 16 rows), "mlp_fused" / "mlp_fused_mma" (the
+    single-launch MLP on CUDA cores / on mma.sync; projections called on their own are unaffected) or None."""
     table = {None: 0, "gemv": _lib.FLAG_FORCE_GEMV, "umma": _lib.FLAG_FORCE_UMMA,
              "umma_smem": _lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A,
-             "umma_scaled": _lib.FLAG_UMMA_SCALED, "mlp_fused": _lib.FLAG_MLP_FUSED}
+             "umma_scaled": _lib.FLAG_UMMA_SCALED, "mlp_fused": _lib.FLAG_MLP_FUSED,
+             "mlp_fused_mma": _lib.FLAG_MLP_FUSED_MMA}
     if name not in table:
         raise ValueError(f"unknown kernel family {name!r}")
     previous = _flags()

@@ -120,9 +120,13 @@ __host__ __device__ inline FusedMlpLayout fused_mlp_layout(int M, int H, int I, 
     l.item_bytes = kFusedItemRows * (H + H / 8);  // rows x (H/2 gate + H/2 up) + rows x 4 x H/32
     int down = (2 * kFusedItemRows * H) / I;      // rows r with r * (I/2 + 2 * I/32) <= item_bytes
     if (down > 2 * kFusedItemRows) down = 2 * kFusedItemRows;
+    if (down > 8) down -= down % 8;  // whole 8-row halves of a 16-row fragment (the warp-MMA variant needs it)
     l.down_rows = down;
     const int floats1 = l.rows1_max * 2 * l.sets1 * M, floats2 = l.rows2_max * l.sets2 * M;
-    const int scratch_bytes = fused_round16(4 * (floats1 > floats2 ? floats1 : floats2));
+    int scratch_floats = floats1 > floats2 ? floats1 : floats2;
+    const int mma_floats = kFusedComputeWarps * 2 * 16 * 8;  // per-item partial tiles of the warp-MMA variant
+    if (M > kFusedMaxRows && scratch_floats < mma_floats) scratch_floats = mma_floats;
+    const int scratch_bytes = fused_round16(4 * scratch_floats);
     const int bars_bytes = 8 * (2 * kFusedMaxSlots) + 16;
     const int fixed = scratch_bytes + bars_bytes + 128;
     int slots = (kFusedSmemBudget - fixed) / l.item_bytes;
@@ -259,6 +263,51 @@ __device__ __forceinline__ void fused_grid_barrier(unsigned long long* slot, int
     fused_compute_sync();
 }
 
+// The producer warp of both kernel variants: streams the CTA's items through the ring.  Weights do
+// not depend on the preceding kernel, so nothing here waits for it.  Lanes 0..5 each issue one copy.
+__device__ __forceinline__ void fused_producer(const FusedMlpParams& p, const FusedMlpLayout& lay, uint8_t* ring,
+                                               uint64_t* full_bar, uint64_t* empty_bar, volatile int* abort_flag,
+                                               int lane, int row1, int n1, int row2, int n2) {
+    const int H = p.H, I = p.I;
+    const int items1 = (n1 + kFusedItemRows - 1) / kFusedItemRows;
+    const int items2 = (n2 + lay.down_rows - 1) / lay.down_rows;
+    const int rb1 = H >> 1, rb2 = I >> 1, sb1 = H >> 5, sb2 = I >> 5;
+    const int slots = lay.slots;
+    for (int it = 0; it < items1 + items2; ++it) {
+        const int slot = it % slots, use = it / slots;
+        if (use > 0 && !ptx::mbar_wait(&empty_bar[slot], (uint32_t)(use - 1) & 1u, abort_flag, kWaitFusedEmpty)) break;
+        __syncwarp();
+        uint8_t* dst = ring + (size_t)slot * lay.item_bytes;
+        if (it < items1) {
+            const int rows = min(kFusedItemRows, n1 - kFusedItemRows * it);
+            const size_t r0 = (size_t)(row1 + kFusedItemRows * it);
+            if (lane == 0) ptx::mbar_expect_tx(&full_bar[slot], (uint32_t)rows * (uint32_t)(2 * rb1 + 4 * sb1));
+            __syncwarp();
+            if (lane < 2) {
+                const uint32_t* src = (lane ? p.up_w : p.gate_w) + r0 * (size_t)(H >> 3);
+                ptx::bulk_load(dst + lane * kFusedItemRows * rb1, src, (uint32_t)rows * rb1, &full_bar[slot]);
+            } else if (lane < 6) {
+                const uint16_t* base = lane == 2 ? p.gate_s : lane == 3 ? p.gate_b : lane == 4 ? p.up_s : p.up_b;
+                ptx::bulk_load(dst + 2 * kFusedItemRows * rb1 + (lane - 2) * kFusedItemRows * sb1,
+                               base + r0 * (size_t)(H >> 6), (uint32_t)rows * sb1, &full_bar[slot]);
+            }
+        } else {
+            const int j = it - items1;
+            const int rows = min(lay.down_rows, n2 - lay.down_rows * j);
+            const size_t r0 = (size_t)(row2 + lay.down_rows * j);
+            if (lane == 0) ptx::mbar_expect_tx(&full_bar[slot], (uint32_t)rows * (uint32_t)(rb2 + 2 * sb2));
+            __syncwarp();
+            if (lane == 0) {
+                ptx::bulk_load(dst, p.down_w + r0 * (size_t)(I >> 3), (uint32_t)rows * rb2, &full_bar[slot]);
+            } else if (lane < 3) {
+                const uint16_t* base = lane == 1 ? p.down_s : p.down_b;
+                ptx::bulk_load(dst + lay.down_rows * rb2 + (lane - 1) * lay.down_rows * sb2,
+                               base + r0 * (size_t)(I >> 6), (uint32_t)rows * sb2, &full_bar[slot]);
+            }
+        }
+    }
+}
+
 template <int kM>
 __global__ void __launch_bounds__(kFusedThreads, 1)
 affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
@@ -299,45 +348,7 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     ptx::griddep_launch_dependents();
 
     if (warp == kFusedComputeWarps) {
-        // ------------------------------------------------------------------ producer warp
-        // Weights do not depend on the preceding kernel, so nothing here waits for it.  Lanes 0..5
-        // each issue one copy of an item.
-        for (int it = 0; it < items1 + items2; ++it) {
-            const int slot = it % slots, use = it / slots;
-            if (use > 0 && !ptx::mbar_wait(&empty_bar[slot], (uint32_t)(use - 1) & 1u, abort_flag, kWaitFusedEmpty)) break;
-            __syncwarp();
-            uint8_t* dst = ring + (size_t)slot * lay.item_bytes;
-#ifdef MT_TIMELINE
-            if (p.timeline != nullptr && blockIdx.x == 0 && lane == 0 && it < 12) p.timeline[30 + it] = clock64();
-#endif
-            if (it < items1) {
-                const int rows = min(kFusedItemRows, n1 - kFusedItemRows * it);
-                const size_t r0 = (size_t)(row1 + kFusedItemRows * it);
-                if (lane == 0) ptx::mbar_expect_tx(&full_bar[slot], (uint32_t)rows * (uint32_t)(2 * rb1 + 4 * sb1));
-                __syncwarp();
-                if (lane < 2) {
-                    const uint32_t* src = (lane ? p.up_w : p.gate_w) + r0 * (size_t)(H >> 3);
-                    ptx::bulk_load(dst + lane * kFusedItemRows * rb1, src, (uint32_t)rows * rb1, &full_bar[slot]);
-                } else if (lane < 6) {
-                    const uint16_t* base = lane == 2 ? p.gate_s : lane == 3 ? p.gate_b : lane == 4 ? p.up_s : p.up_b;
-                    ptx::bulk_load(dst + 2 * kFusedItemRows * rb1 + (lane - 2) * kFusedItemRows * sb1,
-                                   base + r0 * (size_t)(H >> 6), (uint32_t)rows * sb1, &full_bar[slot]);
-                }
-            } else {
-                const int j = it - items1;
-                const int rows = min(lay.down_rows, n2 - lay.down_rows * j);
-                const size_t r0 = (size_t)(row2 + lay.down_rows * j);
-                if (lane == 0) ptx::mbar_expect_tx(&full_bar[slot], (uint32_t)rows * (uint32_t)(rb2 + 2 * sb2));
-                __syncwarp();
-                if (lane == 0) {
-                    ptx::bulk_load(dst, p.down_w + r0 * (size_t)(I >> 3), (uint32_t)rows * rb2, &full_bar[slot]);
-                } else if (lane < 3) {
-                    const uint16_t* base = lane == 1 ? p.down_s : p.down_b;
-                    ptx::bulk_load(dst + lay.down_rows * rb2 + (lane - 1) * lay.down_rows * sb2,
-                                   base + r0 * (size_t)(I >> 6), (uint32_t)rows * sb2, &full_bar[slot]);
-                }
-            }
-        }
+        fused_producer(p, lay, ring, full_bar, empty_bar, abort_flag, lane, row1, n1, row2, n2);
         return;
     }
 
@@ -475,6 +486,306 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     MT_FUSED_STAMP(16);
 }
 
+// ===================================================================================================
+// Warp-MMA variant for four to eight activation rows.
+//
+// The FMA kernel above costs one FMA per weight per row, so it loses to the tensor-core path from four
+// rows on.  Here the multiply runs on mma.sync (m16n8k16, bf16 in, fp32 out): the A fragment is exactly
+// what the nibble unpack produces -- bf16 pairs (128+q_i, 128+q_{i+4}), 7 integer instructions per
+// packed word -- and up to eight activation rows ride in the B fragment for free.  Four MMAs cover one
+// quantisation group (64 k) of 16 weight rows; the group's partial sums P are folded as
+// acc += s * P + (b - 128 s) * X, X = the group's activation sum, so weights stay exact.  mma.sync issues
+// about once per 32 cycles per SM sub-partition on this part, which bounds the kernel near the FMA
+// kernel's one-row time, independent of the row count.  Measured at the Llama-3.2-1B shape it takes
+// 24.6-25.6 us for 1-8 rows, the same as the two-kernel tensor-core path (25.4 us), so it is opt-in
+// (MT_FLAG_MLP_FUSED_MMA) and not part of the default dispatch.
+//
+// Same producer, ring and grid barrier.  The K range is cut into one slice per compute warp; every
+// warp walks all rows of an item for its slice; the warps' partial 16 x 8 tiles meet in shared memory
+// and are added in warp order.  Activation fragments hold element pairs in the order the unpack emits
+// them: (e0,e4), (e1,e5), (e2,e6), (e3,e7).
+
+constexpr int kFusedMmaMaxRows = 8;
+constexpr int kFusedMmaMaxGroups1 = 4;  // quantisation groups of H per warp that fit in registers
+
+__device__ __forceinline__ uint4 permute_for_fragment(uint4 v) {
+    uint4 o;
+    o.x = __byte_perm(v.x, v.z, 0x5410);
+    o.y = __byte_perm(v.x, v.z, 0x7632);
+    o.z = __byte_perm(v.y, v.w, 0x5410);
+    o.w = __byte_perm(v.y, v.w, 0x7632);
+    return o;
+}
+
+// Lane (g, t) loads column g's 16 activations k = 64 group + 16 t .. +15 as two fragment registers
+// sets, and returns the group's sums of columns 2t and 2t+1 (x0, x1) gathered by shuffles.
+template <bool kFromL2>
+__device__ __forceinline__ void load_group_fragments(const uint16_t* column, bool active, int group, int t, uint4& bx0,
+                                                     uint4& bx1, float& x0, float& x1) {
+    uint4 v0 = make_uint4(0, 0, 0, 0), v1 = make_uint4(0, 0, 0, 0);
+    if (active) {
+        const uint16_t* from = column + group * 64 + t * 16;
+        v0 = kFromL2 ? ptx::ld_global_l2_u4(from) : ptx::ld_global_dependent_u4(from);
+        v1 = kFromL2 ? ptx::ld_global_l2_u4(from + 8) : ptx::ld_global_dependent_u4(from + 8);
+    }
+    bx0 = permute_for_fragment(v0);
+    bx1 = permute_for_fragment(v1);
+    const uint32_t words[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float partial = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        partial += bf16_lo(words[i]);
+        partial += bf16_hi(words[i]);
+    }
+    partial += __shfl_xor_sync(0xFFFFFFFFu, partial, 1);
+    partial += __shfl_xor_sync(0xFFFFFFFFu, partial, 2);  // every lane of fragment row g holds column g's sum
+    x0 = __shfl_sync(0xFFFFFFFFu, partial, 8 * t);        // lane 4 * (2t)
+    x1 = __shfl_sync(0xFFFFFFFFu, partial, 8 * t + 4);    // lane 4 * (2t + 1)
+}
+
+// One quantisation group of one 16-row tile: rows g (lower) and g+8 (upper) of the fragment.
+template <bool kUpper>
+__device__ __forceinline__ void mma_group(const uint8_t* lower, const uint8_t* upper, uint32_t scale_lo, uint32_t bias_lo,
+                                          uint32_t scale_hi, uint32_t bias_hi, const uint4& bx0, const uint4& bx1,
+                                          float x0, float x1, float (&acc)[4]) {
+    const uint2 lo = *reinterpret_cast<const uint2*>(lower);
+    uint32_t l0[4], l1[4], h0[4] = {0, 0, 0, 0}, h1[4] = {0, 0, 0, 0};
+    unpack_word_offset128(lo.x, l0);
+    unpack_word_offset128(lo.y, l1);
+    if constexpr (kUpper) {
+        const uint2 hi = *reinterpret_cast<const uint2*>(upper);
+        unpack_word_offset128(hi.x, h0);
+        unpack_word_offset128(hi.y, h1);
+    }
+    float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    ptx::mma_bf16_m16n8k16(d, l0[0], h0[0], l0[1], h0[1], bx0.x, bx0.y);
+    ptx::mma_bf16_m16n8k16(d, l0[2], h0[2], l0[3], h0[3], bx0.z, bx0.w);
+    ptx::mma_bf16_m16n8k16(d, l1[0], h1[0], l1[1], h1[1], bx1.x, bx1.y);
+    ptx::mma_bf16_m16n8k16(d, l1[2], h1[2], l1[3], h1[3], bx1.z, bx1.w);
+    const float s_lo = bf16_bits_to_f32(scale_lo);
+    const float o_lo = fmaf(-128.0f, s_lo, bf16_bits_to_f32(bias_lo));  // undoes the 128 in 128+q
+    acc[0] = fmaf(s_lo, d[0], fmaf(o_lo, x0, acc[0]));
+    acc[1] = fmaf(s_lo, d[1], fmaf(o_lo, x1, acc[1]));
+    if constexpr (kUpper) {
+        const float s_hi = bf16_bits_to_f32(scale_hi);
+        const float o_hi = fmaf(-128.0f, s_hi, bf16_bits_to_f32(bias_hi));
+        acc[2] = fmaf(s_hi, d[2], fmaf(o_hi, x0, acc[2]));
+        acc[3] = fmaf(s_hi, d[3], fmaf(o_hi, x1, acc[3]));
+    }
+}
+
+__global__ void __launch_bounds__(kFusedThreads, 1)
+affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
+    extern __shared__ uint8_t fused_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fused_smem_raw) + 127) & ~(uintptr_t)127);
+    const int grid = gridDim.x, cta = blockIdx.x;
+    const int M = p.M, H = p.H, I = p.I;
+    const FusedMlpLayout lay = fused_mlp_layout(kFusedMmaMaxRows, H, I, grid);
+    uint8_t* ring = smem + lay.ring;
+    float* scratch = reinterpret_cast<float*>(smem + lay.scratch);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + lay.bars);
+    uint64_t* empty_bar = full_bar + kFusedMaxSlots;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kFusedMaxSlots);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    const int row1 = (int)((unsigned)I * (unsigned)cta / (unsigned)grid);
+    const int n1 = (int)((unsigned)I * (unsigned)(cta + 1) / (unsigned)grid) - row1;
+    const int row2 = (int)((unsigned)H * (unsigned)cta / (unsigned)grid);
+    const int n2 = (int)((unsigned)H * (unsigned)(cta + 1) / (unsigned)grid) - row2;
+    const int items1 = (n1 + kFusedItemRows - 1) / kFusedItemRows;
+    const int items2 = (n2 + lay.down_rows - 1) / lay.down_rows;
+    const int rb1 = H >> 1, rb2 = I >> 1, sb1 = H >> 5, sb2 = I >> 5;
+    const int slots = lay.slots;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kFusedMaxSlots; ++i) {
+            ptx::mbar_init(&full_bar[i], 1);
+            ptx::mbar_init(&empty_bar[i], kFusedComputeWarps);
+        }
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+    }
+    __syncthreads();
+    ptx::griddep_launch_dependents();
+    if (warp == kFusedComputeWarps) {
+        fused_producer(p, lay, ring, full_bar, empty_bar, abort_flag, lane, row1, n1, row2, n2);
+        return;
+    }
+
+    // ---------------------------------------------------------------------- compute warps
+    ptx::griddep_wait();  // the activations and the residual are the preceding kernel's output
+    float residual_value = 0.0f;
+    if ((int)threadIdx.x < n2 * M && p.residual) {
+        const int row = threadIdx.x / M, m = threadIdx.x - row * M;
+        residual_value = bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.residual + (size_t)m * H + row2 + row));
+    }
+    const bool active = g < M;  // fragment column g carries activation row g
+    bool alive = true;
+    {
+        // ------------------------------------------------------------------ gate | up
+        const int groups = (H >> 6) / kFusedComputeWarps;  // quantisation groups in this warp's K slice (<= 4)
+        const int group0 = warp * groups;
+        uint4 bx0[kFusedMmaMaxGroups1], bx1[kFusedMmaMaxGroups1];
+        float x0[kFusedMmaMaxGroups1], x1[kFusedMmaMaxGroups1];
+#pragma unroll
+        for (int gi = 0; gi < kFusedMmaMaxGroups1; ++gi)
+            if (gi < groups) load_group_fragments<false>(p.x + (size_t)(active ? g : 0) * H, active, group0 + gi, t, bx0[gi], bx1[gi], x0[gi], x1[gi]);
+        for (int it = 0; it < items1; ++it) {
+            const int slot = it % slots, use = it / slots;
+            if (alive && !ptx::mbar_wait(&full_bar[slot], (uint32_t)use & 1u, abort_flag, kWaitFusedFull)) alive = false;
+            alive = __all_sync(0xFFFFFFFFu, alive);  // the MMAs and shuffles below need the whole warp or none of it
+            const uint8_t* item = ring + (size_t)slot * lay.item_bytes;
+            const uint8_t* tables = item + 2 * kFusedItemRows * rb1;
+            const int rows_here = min(kFusedItemRows, n1 - kFusedItemRows * it);
+            const bool upper = rows_here > 8;
+            float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+            if (alive) {
+#pragma unroll
+                for (int matrix = 0; matrix < 2; ++matrix) {
+#pragma unroll
+                    for (int gi = 0; gi < kFusedMmaMaxGroups1; ++gi) {
+                        if (gi < groups) {
+                            const int group = group0 + gi;
+                            const uint8_t* lower = item + (matrix * kFusedItemRows + g) * rb1 + group * 32 + t * 8;
+                            const uint8_t* sc = tables + ((2 * matrix) * kFusedItemRows + g) * sb1 + group * 2;
+                            const uint8_t* bi = tables + ((2 * matrix + 1) * kFusedItemRows + g) * sb1 + group * 2;
+                            const uint32_t scale_lo = *reinterpret_cast<const uint16_t*>(sc);
+                            const uint32_t bias_lo = *reinterpret_cast<const uint16_t*>(bi);
+                            if (upper) {
+                                const uint32_t scale_hi = *reinterpret_cast<const uint16_t*>(sc + 8 * sb1);
+                                const uint32_t bias_hi = *reinterpret_cast<const uint16_t*>(bi + 8 * sb1);
+                                mma_group<true>(lower, lower + 8 * rb1, scale_lo, bias_lo, scale_hi, bias_hi, bx0[gi],
+                                                bx1[gi], x0[gi], x1[gi], acc[matrix]);
+                            } else {
+                                mma_group<false>(lower, nullptr, scale_lo, bias_lo, 0, 0, bx0[gi], bx1[gi], x0[gi],
+                                                 x1[gi], acc[matrix]);
+                            }
+                        }
+                    }
+                }
+            }
+            if (it + slots < items1 + items2) {
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
+            }
+            // scratch[((warp * 2 + matrix) * 16 + row) * 8 + column]
+#pragma unroll
+            for (int matrix = 0; matrix < 2; ++matrix) {
+                float* tile = scratch + (size_t)((warp * 2 + matrix) * 16) * 8;
+                *reinterpret_cast<float2*>(tile + g * 8 + 2 * t) = make_float2(acc[matrix][0], acc[matrix][1]);
+                *reinterpret_cast<float2*>(tile + (g + 8) * 8 + 2 * t) = make_float2(acc[matrix][2], acc[matrix][3]);
+            }
+            fused_compute_sync();
+            for (int idx = threadIdx.x; idx < rows_here * M; idx += kFusedComputeThreads) {
+                const int row = idx / M, m = idx - row * M;
+                float gate = 0.0f, up = 0.0f;
+                for (int w = 0; w < kFusedComputeWarps; ++w) {
+                    gate += scratch[((w * 2 + 0) * 16 + row) * 8 + m];
+                    up += scratch[((w * 2 + 1) * 16 + row) * 8 + m];
+                }
+                p.hidden[(size_t)m * I + row1 + kFusedItemRows * it + row] = f32_to_bf16_bits(swiglu_f32(gate, up));
+            }
+            fused_compute_sync();
+        }
+    }
+    fused_grid_barrier(p.barrier, grid, abort_flag);
+    {
+        // ------------------------------------------------------------------ down
+        const int groups = (I >> 6) / kFusedComputeWarps;
+        const int group0 = warp * groups;
+        const uint16_t* column = p.hidden + (size_t)(active ? g : 0) * I;
+        const int tiles = (n2 + 15) >> 4;
+        int released = 0;  // down items handed back to the producer so far
+        for (int tile = 0; tile < tiles; ++tile) {
+            // Rows 16 tile + g (lower) and 16 tile + 8 + g (upper) of this CTA's down rows, wherever
+            // their items sit in the ring.
+            const int r_lo = 16 * tile, r_hi = 16 * tile + 8;
+            const bool upper = r_hi < n2;
+            const int j_lo = r_lo / lay.down_rows, j_hi = upper ? r_hi / lay.down_rows : j_lo;
+            for (int j = j_lo; j <= j_hi; ++j) {
+                const int it = items1 + j;
+                if (alive && !ptx::mbar_wait(&full_bar[it % slots], (uint32_t)(it / slots) & 1u, abort_flag, kWaitFusedFull))
+                    alive = false;
+            }
+            alive = __all_sync(0xFFFFFFFFu, alive);
+            const uint8_t* item_lo = ring + (size_t)((items1 + j_lo) % slots) * lay.item_bytes;
+            const uint8_t* item_hi = ring + (size_t)((items1 + j_hi) % slots) * lay.item_bytes;
+            const int local_lo = r_lo - j_lo * lay.down_rows + g, local_hi = r_hi - j_hi * lay.down_rows + g;
+            const uint8_t* lower = item_lo + local_lo * rb2 + t * 8;
+            const uint8_t* upper_row = item_hi + local_hi * rb2 + t * 8;
+            const uint8_t* sc_lo = item_lo + lay.down_rows * rb2 + local_lo * sb2;
+            const uint8_t* sc_hi = item_hi + lay.down_rows * rb2 + local_hi * sb2;
+            const int table = lay.down_rows * sb2;  // biases follow the scales
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (alive) {
+                uint4 bx0, bx1, nx0, nx1;
+                float x0, x1, y0, y1;
+                load_group_fragments<true>(column, active, group0, t, bx0, bx1, x0, x1);
+                for (int gi = 0; gi < groups; ++gi) {
+                    const int group = group0 + gi;
+                    if (gi + 1 < groups) load_group_fragments<true>(column, active, group + 1, t, nx0, nx1, y0, y1);
+                    const uint32_t scale_lo = *reinterpret_cast<const uint16_t*>(sc_lo + group * 2);
+                    const uint32_t bias_lo = *reinterpret_cast<const uint16_t*>(sc_lo + table + group * 2);
+                    if (upper) {
+                        const uint32_t scale_hi = *reinterpret_cast<const uint16_t*>(sc_hi + group * 2);
+                        const uint32_t bias_hi = *reinterpret_cast<const uint16_t*>(sc_hi + table + group * 2);
+                        mma_group<true>(lower + group * 32, upper_row + group * 32, scale_lo, bias_lo, scale_hi, bias_hi, bx0,
+                                        bx1, x0, x1, acc);
+                    } else {
+                        mma_group<false>(lower + group * 32, nullptr, scale_lo, bias_lo, 0, 0, bx0, bx1, x0, x1, acc);
+                    }
+                    bx0 = nx0; bx1 = nx1; x0 = y0; x1 = y1;
+                }
+            }
+            // Hand back the items that end inside this tile.
+            while (released < items2 && (released + 1) * lay.down_rows <= 16 * (tile + 1)) {
+                const int it = items1 + released;
+                if (it + slots < items1 + items2) {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&empty_bar[it % slots]);
+                }
+                ++released;
+            }
+            float* part = scratch + (size_t)(warp * 16) * 8;  // scratch[(warp * 16 + row) * 8 + column]
+            *reinterpret_cast<float2*>(part + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
+            *reinterpret_cast<float2*>(part + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
+            fused_compute_sync();
+            const int rows_here = min(16, n2 - 16 * tile);
+            for (int idx = threadIdx.x; idx < rows_here * M; idx += kFusedComputeThreads) {
+                const int row = idx / M, m = idx - row * M;
+                float v = 0.0f;
+                for (int w = 0; w < kFusedComputeWarps; ++w) v += scratch[(w * 16 + row) * 8 + m];
+                // The residual was fetched by thread (16 tile + row) * M + m, which is this one only in the
+                // first tile; later tiles read it here.
+                const size_t at = (size_t)m * H + row2 + 16 * tile + row;
+                float extra = residual_value;
+                if (tile > 0) extra = p.residual ? bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.residual + at)) : 0.0f;
+                p.out[at] = f32_to_bf16_bits(v + extra);
+            }
+            fused_compute_sync();
+        }
+    }
+}
+
+// Whether the warp-MMA variant serves this problem.
+inline bool fused_mlp_mma_applicable(const FusedMlpParams& p, int sm_count) {
+    if (p.M < 1 || p.M > kFusedMmaMaxRows || sm_count < 1) return false;
+    if (p.H < 512 || p.H % (64 * kFusedComputeWarps) || (p.H >> 6) / kFusedComputeWarps > kFusedMmaMaxGroups1) return false;
+    if (p.I < 512 || p.I % (64 * kFusedComputeWarps)) return false;
+    const FusedMlpLayout lay = fused_mlp_layout(kFusedMmaMaxRows, p.H, p.I, sm_count);
+    if (lay.slots < 2 || lay.down_rows < 8 || lay.down_rows % 8) return false;
+    if (16 * p.M > kFusedComputeThreads) return false;
+    if (lay.total + 128 > kFusedSmemBudget) return false;
+    const void* pointers[] = {p.x, p.gate_w, p.up_w, p.down_w, p.gate_s, p.gate_b, p.up_s, p.up_b, p.down_s, p.down_b,
+                              p.hidden};
+    for (const void* ptr : pointers)
+        if (!aligned_to(ptr, 16)) return false;
+    return true;
+}
+
 // Whether the fused kernel serves this problem on a device with `sm_count` SMs.
 inline bool fused_mlp_applicable(const FusedMlpParams& p, int sm_count) {
     if (p.M < 1 || p.M > kFusedMaxRows || sm_count < 1) return false;
@@ -496,11 +807,11 @@ inline bool fused_mlp_applicable(const FusedMlpParams& p, int sm_count) {
 // 0 = untried, 1 = programmatic dependent launch accepted together with a cooperative launch, -1 = refused.
 static int g_fused_pdl_state[64] = {};
 
-template <int kM>
-inline int launch_mlp_fused_rows(const FusedMlpParams& params, int sm_count, int device, cudaStream_t stream) {
+// `kKind` only separates the per-kernel static state (1..4 = FMA kernel rows, 0 = warp-MMA kernel).
+template <int kKind>
+inline int launch_mlp_fused_kernel(void (*kernel)(const FusedMlpParams), int smem, const FusedMlpParams& params,
+                                   int sm_count, int device, cudaStream_t stream) {
     static bool configured[64] = {};
-    auto kernel = affine_mlp_fused_kernel<kM>;
-    const int smem = fused_mlp_layout(kM, params.H, params.I, sm_count).total + 128;
     if (!configured[device]) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmemBudget) != cudaSuccess)
             return MT_ERR_LAUNCH;
@@ -538,8 +849,14 @@ inline int launch_mlp_fused_rows(const FusedMlpParams& params, int sm_count, int
     return cudaLaunchKernelEx(&config, kernel, params) == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
 }
 
-// Caller has checked fused_mlp_applicable().
-inline int launch_mlp_fused(FusedMlpParams params, int sm_count, cudaStream_t stream) {
+template <int kM>
+inline int launch_mlp_fused_rows(const FusedMlpParams& params, int sm_count, int device, cudaStream_t stream) {
+    const int smem = fused_mlp_layout(kM, params.H, params.I, sm_count).total + 128;
+    return launch_mlp_fused_kernel<kM>(affine_mlp_fused_kernel<kM>, smem, params, sm_count, device, stream);
+}
+
+// Caller has checked fused_mlp_applicable(), or fused_mlp_mma_applicable() when `mma` is set.
+inline int launch_mlp_fused(FusedMlpParams params, int sm_count, bool mma, cudaStream_t stream) {
     static unsigned long long* slots[64] = {};
     static unsigned int launches = 0;
     int device = 0;
@@ -552,6 +869,10 @@ inline int launch_mlp_fused(FusedMlpParams params, int sm_count, cudaStream_t st
         slots[device] = static_cast<unsigned long long*>(address);
     }
     params.barrier = slots[device] + (__atomic_fetch_add(&launches, 1u, __ATOMIC_RELAXED) % kFusedBarrierSlots);
+    if (mma) {
+        const int smem = fused_mlp_layout(kFusedMmaMaxRows, params.H, params.I, sm_count).total + 128;
+        return launch_mlp_fused_kernel<0>(affine_mlp_fused_mma_kernel, smem, params, sm_count, device, stream);
+    }
     switch (params.M) {
         case 1: return launch_mlp_fused_rows<1>(params, sm_count, device, stream);
         case 2: return launch_mlp_fused_rows<2>(params, sm_count, device, stream);

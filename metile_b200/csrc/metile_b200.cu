@@ -246,7 +246,7 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
         return MT_ERR_WORKSPACE;
     // A handful of rows: the whole MLP as one cooperative launch when the shape fits it.  Any flag
     // that pins a kernel family keeps the two-kernel path; MT_FLAG_MLP_FUSED insists on this one.
-    if (flags == 0 || (flags & MT_FLAG_MLP_FUSED)) {
+    if (flags == 0 || (flags & (MT_FLAG_MLP_FUSED | MT_FLAG_MLP_FUSED_MMA))) {
         if (!x || !gate_w || !gate_scales || !gate_biases || !up_w || !up_scales || !up_biases || !down_w ||
             !down_scales || !down_biases || !out)
             return MT_ERR_NULL;
@@ -271,15 +271,19 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
         params.H = H;
         params.I = I;
         const int sms = device_sm_count();
-        if ((flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms)) {
-            const int fused_rc = launch_mlp_fused(params, sms, static_cast<cudaStream_t>(stream));
+        // Up to kFusedDefaultRows rows: the FMA kernel.  The warp-MMA kernel (to eight rows) only on request.
+        const bool want_mma = (flags & MT_FLAG_MLP_FUSED_MMA) != 0;
+        const bool fma = !want_mma && (flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms);
+        const bool mma = want_mma && fused_mlp_mma_applicable(params, sms);  // measured no faster than the tensor path: opt-in
+        if (fma || mma) {
+            const int fused_rc = launch_mlp_fused(params, sms, mma, static_cast<cudaStream_t>(stream));
             // A cooperative launch is refused when the whole grid cannot be resident (a GPU shared with
             // another context, a carve-out that leaves too little shared memory).  Nothing was queued:
             // the default dispatch then takes the two-kernel path; an explicit request reports it.
-            if (fused_rc != MT_ERR_LAUNCH || (flags & MT_FLAG_MLP_FUSED)) return fused_rc;
+            if (fused_rc != MT_ERR_LAUNCH || flags) return fused_rc;
             cudaGetLastError();
         }
-        if (flags & MT_FLAG_MLP_FUSED) return MT_ERR_SHAPE;
+        if (flags) return MT_ERR_SHAPE;
     }
     rc = mt_affine_swiglu(x, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, workspace, M, H, I,
                           group_size, bits, flags, stream);
@@ -320,14 +324,16 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
 
 int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags) {
     if (M <= 0) return 0;
-    if (flags != 0 && !(flags & MT_FLAG_MLP_FUSED)) return 2;
+    if (flags != 0 && !(flags & (MT_FLAG_MLP_FUSED | MT_FLAG_MLP_FUSED_MMA))) return 2;
     FusedMlpParams params = {};
     params.M = M;
     params.H = H;
     params.I = I;
     const int sms = device_sm_count();
-    if (!flags && M > kFusedDefaultRows) return 2;
-    return sms > 0 && fused_mlp_applicable(params, sms) ? 1 : 2;  // null pointers count as aligned
+    if (sms <= 0) return 2;
+    const bool want_mma = (flags & MT_FLAG_MLP_FUSED_MMA) != 0;
+    if (!want_mma && (flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms)) return 1;  // null pointers count as aligned
+    return want_mma && fused_mlp_mma_applicable(params, sms) ? 1 : 2;
 }
 
 size_t mt_affine_mlp_static_max_bytes(void) { return kStaticHiddenBytes; }

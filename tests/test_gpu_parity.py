@@ -229,7 +229,6 @@ def test_single_launch_mlp_up_to_four_rows(cuda_device, hidden, inter):
     for rows in (1, 2, 3):
         assert library.mt_affine_mlp_launches(rows, hidden, inter, 0) == 1
         assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], "default dispatch is the single-launch kernel")
-    assert library.mt_affine_mlp_launches(4, hidden, inter, 0) == 2
     assert library.mt_affine_mlp_launches(4, hidden, inter, _lib.FLAG_MLP_FUSED) == 1
     # Without a residual, and against the two-kernel path (different fp32 order, same tolerance).
     no_residual = B.mlx_affine_mlp_executor(x, *gate, *up, *down, None)
@@ -241,6 +240,30 @@ def test_single_launch_mlp_up_to_four_rows(cuda_device, hidden, inter):
     assert_within(full, f32(y_two), rel=4e-3, what="single-launch vs two-kernel path")
 
 
+@pytest.mark.parametrize("hidden,inter", [(2048, 8192), (1024, 2048), (1024, 1024), (2048, 4096), (512, 1536)])
+def test_single_launch_mlp_on_warp_mma_up_to_eight_rows(cuda_device, hidden, inter):
+    """The warp-MMA variant of the single-launch MLP (opt-in, up to eight rows): exact weights,
+    oracle at the MLP tolerance, rows bit-identical alone or in a batch of eight, repeatable."""
+    gate, up, down = synth.mlp_weights(320, hidden, inter, cuda_device)
+    triples_np = [triple_np(t) for t in (gate, up, down)]
+    x = synth.activations(5, 8, hidden, cuda_device)
+    res = synth.activations(6, 8, hidden, cuda_device)
+    execute = B.mlx_affine_mlp_executor(x, *gate, *up, *down, res)
+    library = _lib.load()
+    with B.force_kernel("mlp_fused_mma"):
+        full = execute(x, res)
+        assert_bit_equal(execute(x, res), full, "repeat launch")
+        for rows in (1, 3, 4, 5, 7):
+            assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], f"{rows} rows alone vs in a batch of 8")
+        assert_bit_equal(execute(x[7:8], res[7:8]), full[7:8], "last row alone")
+        y_plain = B.mlx_affine_mlp_executor(x, *gate, *up, *down, None)(x, None)
+    assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=4e-3, what=f"warp-MMA MLP {hidden}x{inter}")
+    assert_within(y_plain, A.mlp(f32(x), *triples_np, None), rel=4e-3, what="warp-MMA MLP, no residual")
+    assert library.mt_affine_mlp_launches(8, hidden, inter, _lib.FLAG_MLP_FUSED_MMA) == 1
+    assert library.mt_affine_mlp_launches(8, hidden, inter, 0) == 2  # opt-in: no faster than the tensor path
+    assert library.mt_affine_mlp_launches(9, hidden, inter, _lib.FLAG_MLP_FUSED_MMA) == 2
+
+
 def test_single_launch_mlp_refuses_what_it_does_not_serve(cuda_device):
     gate, up, down = synth.mlp_weights(301, 2048, 8192, cuda_device)
     x = synth.activations(5, 5, 2048, cuda_device)
@@ -248,6 +271,10 @@ def test_single_launch_mlp_refuses_what_it_does_not_serve(cuda_device):
     with B.force_kernel("mlp_fused"):
         with pytest.raises(ValueError):
             execute(x, x)  # five rows
+    x9 = synth.activations(5, 9, 2048, cuda_device)
+    with B.force_kernel("mlp_fused_mma"):
+        with pytest.raises(ValueError):
+            B.mlx_affine_mlp_executor(x9, *gate, *up, *down, x9)(x9, x9)  # nine rows
     gate, up, down = synth.mlp_weights(302, 1536, 1024, cuda_device)
     x = synth.activations(5, 1, 1536, cuda_device)
     execute = B.mlx_affine_mlp_executor(x, *gate, *up, *down, x)
