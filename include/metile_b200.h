@@ -18,7 +18,8 @@
  * Errors are detected before any GPU work is queued.  There is no CPU fallback.
  *
  * `flags`: 0 selects the kernel by row count (CUDA-core GEMV for M = 1, tcgen05 MMA above;
- * mt_affine_mlp with M <= 3 runs as one launch when the shape allows, see MT_FLAG_MLP_FUSED).
+ * mt_affine_mlp with M <= 8 runs as one launch when the shape allows, see MT_FLAG_MLP_FUSED and
+ * MT_FLAG_MLP_FUSED_MMA).
  *   MT_FLAG_FORCE_GEMV (1)   CUDA-core GEMV (M <= 8)
  *   MT_FLAG_FORCE_UMMA (2)   tcgen05 path for any M (one accumulation order for every M:
  *                            use it when rows must be bit-identical across batch sizes 1..128)
@@ -34,8 +35,7 @@
  *                            two-kernel path if the driver refuses the cooperative launch.
  *   MT_FLAG_MLP_FUSED_MMA (128) mt_affine_mlp: insist on the warp-MMA variant of the single-launch
  *                            kernel (M <= 8, H in {512, 1024, 1536, 2048}, I a multiple of 512); -1
- *                            when it does not apply.  Opt-in only: measured no faster than the
- *                            two-kernel tensor-core path.
+ *                            when it does not apply.  With flags = 0 it serves M = 4 ... 8.
  */
 #ifndef METILE_B200_H
 #define METILE_B200_H
@@ -122,8 +122,8 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
 
 /* How many kernels mt_affine_mlp queues for this problem on the current device with 16-byte
  * aligned operands: 1 when a single-launch kernel serves it (up to three rows on CUDA cores, four with
- * MT_FLAG_MLP_FUSED, H and I in {1024, 2048, 4096, 8192}; up to eight rows on mma.sync with
- * MT_FLAG_MLP_FUSED_MMA, H <= 2048), else 2 (gate|up
+ * MT_FLAG_MLP_FUSED, H and I in {1024, 2048, 4096, 8192}; four to eight rows on mma.sync, H <= 2048),
+ * else 2 (gate|up
  * SwiGLU, then down); 0 for M <= 0.  No counterpart in the reference project; used for launch
  * accounting. */
 int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags);

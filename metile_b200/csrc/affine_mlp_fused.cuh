@@ -496,9 +496,10 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
 // quantisation group (64 k) of 16 weight rows; the group's partial sums P are folded as
 // acc += s * P + (b - 128 s) * X, X = the group's activation sum, so weights stay exact.  mma.sync issues
 // about once per 32 cycles per SM sub-partition on this part, which bounds the kernel near the FMA
-// kernel's one-row time, independent of the row count.  Measured at the Llama-3.2-1B shape it takes
-// 24.6-25.6 us for 1-8 rows, the same as the two-kernel tensor-core path (25.4 us), so it is opt-in
-// (MT_FLAG_MLP_FUSED_MMA) and not part of the default dispatch.
+// kernel's one-row time, independent of the row count.  The four MMAs of a group are a dependent chain,
+// so four (block, group) pairs are issued round-robin; with one chain at a time the kernel took 25 us.
+// Measured at the Llama-3.2-1B shape: 21.5-22.5 us for 1-8 rows against 25.4-25.8 us on the two-kernel
+// tensor-core path, so it is the default for four to eight rows.
 //
 // Same producer, ring and grid barrier.  The K range is cut into one slice per compute warp; every
 // warp walks all rows of an item for its slice; the warps' partial 16 x 8 tiles meet in shared memory
@@ -543,34 +544,56 @@ __device__ __forceinline__ void load_group_fragments(const uint16_t* column, boo
     x1 = __shfl_sync(0xFFFFFFFFu, partial, 8 * t + 4);    // lane 4 * (2t + 1)
 }
 
-// One quantisation group of one 16-row tile: rows g (lower) and g+8 (upper) of the fragment.
-template <bool kUpper>
-__device__ __forceinline__ void mma_group(const uint8_t* lower, const uint8_t* upper, uint32_t scale_lo, uint32_t bias_lo,
-                                          uint32_t scale_hi, uint32_t bias_hi, const uint4& bx0, const uint4& bx1,
-                                          float x0, float x1, float (&acc)[4]) {
-    const uint2 lo = *reinterpret_cast<const uint2*>(lower);
-    uint32_t l0[4], l1[4], h0[4] = {0, 0, 0, 0}, h1[4] = {0, 0, 0, 0};
-    unpack_word_offset128(lo.x, l0);
-    unpack_word_offset128(lo.y, l1);
-    if constexpr (kUpper) {
-        const uint2 hi = *reinterpret_cast<const uint2*>(upper);
-        unpack_word_offset128(hi.x, h0);
-        unpack_word_offset128(hi.y, h1);
+// kN independent (16-row block, quantisation group) pairs at once: rows g (lower) and g+8 (upper) of
+// each fragment.  The four MMAs of a pair form a dependent chain (they accumulate one group's partial
+// sums), so the pairs' MMAs are issued round-robin to keep the tensor pipe fed.
+struct MmaOperand {
+    const uint8_t* lower;   // this lane's 8 packed bytes of row g for the group
+    const uint8_t* upper;   // ... of row g+8 (ignored without kUpper)
+    uint32_t scale_lo, bias_lo, scale_hi, bias_hi;  // bf16 bits
+};
+
+template <int kN, bool kUpper>
+__device__ __forceinline__ void mma_groups(const MmaOperand (&op)[kN], const uint4 (&bx0)[kN], const uint4 (&bx1)[kN],
+                                           const float (&x0)[kN], const float (&x1)[kN], float* const (&acc)[kN]) {
+    uint32_t lo[kN][8], hi[kN][8];
+#pragma unroll
+    for (int i = 0; i < kN; ++i) {
+        const uint2 l = *reinterpret_cast<const uint2*>(op[i].lower);
+        unpack_word_offset128(l.x, &lo[i][0]);
+        unpack_word_offset128(l.y, &lo[i][4]);
+        if constexpr (kUpper) {
+            const uint2 h = *reinterpret_cast<const uint2*>(op[i].upper);
+            unpack_word_offset128(h.x, &hi[i][0]);
+            unpack_word_offset128(h.y, &hi[i][4]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) hi[i][k] = 0u;
+        }
     }
-    float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    ptx::mma_bf16_m16n8k16(d, l0[0], h0[0], l0[1], h0[1], bx0.x, bx0.y);
-    ptx::mma_bf16_m16n8k16(d, l0[2], h0[2], l0[3], h0[3], bx0.z, bx0.w);
-    ptx::mma_bf16_m16n8k16(d, l1[0], h1[0], l1[1], h1[1], bx1.x, bx1.y);
-    ptx::mma_bf16_m16n8k16(d, l1[2], h1[2], l1[3], h1[3], bx1.z, bx1.w);
-    const float s_lo = bf16_bits_to_f32(scale_lo);
-    const float o_lo = fmaf(-128.0f, s_lo, bf16_bits_to_f32(bias_lo));  // undoes the 128 in 128+q
-    acc[0] = fmaf(s_lo, d[0], fmaf(o_lo, x0, acc[0]));
-    acc[1] = fmaf(s_lo, d[1], fmaf(o_lo, x1, acc[1]));
-    if constexpr (kUpper) {
-        const float s_hi = bf16_bits_to_f32(scale_hi);
-        const float o_hi = fmaf(-128.0f, s_hi, bf16_bits_to_f32(bias_hi));
-        acc[2] = fmaf(s_hi, d[2], fmaf(o_hi, x0, acc[2]));
-        acc[3] = fmaf(s_hi, d[3], fmaf(o_hi, x1, acc[3]));
+    float d[kN][4];
+#pragma unroll
+    for (int i = 0; i < kN; ++i) d[i][0] = d[i][1] = d[i][2] = d[i][3] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kN; ++i) ptx::mma_bf16_m16n8k16(d[i], lo[i][0], hi[i][0], lo[i][1], hi[i][1], bx0[i].x, bx0[i].y);
+#pragma unroll
+    for (int i = 0; i < kN; ++i) ptx::mma_bf16_m16n8k16(d[i], lo[i][2], hi[i][2], lo[i][3], hi[i][3], bx0[i].z, bx0[i].w);
+#pragma unroll
+    for (int i = 0; i < kN; ++i) ptx::mma_bf16_m16n8k16(d[i], lo[i][4], hi[i][4], lo[i][5], hi[i][5], bx1[i].x, bx1[i].y);
+#pragma unroll
+    for (int i = 0; i < kN; ++i) ptx::mma_bf16_m16n8k16(d[i], lo[i][6], hi[i][6], lo[i][7], hi[i][7], bx1[i].z, bx1[i].w);
+#pragma unroll
+    for (int i = 0; i < kN; ++i) {
+        const float s_lo = bf16_bits_to_f32(op[i].scale_lo);
+        const float o_lo = fmaf(-128.0f, s_lo, bf16_bits_to_f32(op[i].bias_lo));  // undoes the 128 in 128+q
+        acc[i][0] = fmaf(s_lo, d[i][0], fmaf(o_lo, x0[i], acc[i][0]));
+        acc[i][1] = fmaf(s_lo, d[i][1], fmaf(o_lo, x1[i], acc[i][1]));
+        if constexpr (kUpper) {
+            const float s_hi = bf16_bits_to_f32(op[i].scale_hi);
+            const float o_hi = fmaf(-128.0f, s_hi, bf16_bits_to_f32(op[i].bias_hi));
+            acc[i][2] = fmaf(s_hi, d[i][2], fmaf(o_hi, x0[i], acc[i][2]));
+            acc[i][3] = fmaf(s_hi, d[i][3], fmaf(o_hi, x1[i], acc[i][3]));
+        }
     }
 }
 
@@ -641,25 +664,46 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
             const bool upper = rows_here > 8;
             float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
             if (alive) {
+                // Two groups x (gate, up) = four independent MMA chains per step.  A second group past
+                // the slice's end repeats the first one into a discarded accumulator.
 #pragma unroll
-                for (int matrix = 0; matrix < 2; ++matrix) {
+                for (int gi = 0; gi < kFusedMmaMaxGroups1; gi += 2) {
+                    if (gi < groups) {
+                        const bool second = gi + 1 < groups;
+                        float discard[4];
+                        MmaOperand op[4];
+                        uint4 fx0[4], fx1[4];
+                        float fs0[4], fs1[4];
+                        float* into[4];
 #pragma unroll
-                    for (int gi = 0; gi < kFusedMmaMaxGroups1; ++gi) {
-                        if (gi < groups) {
-                            const int group = group0 + gi;
-                            const uint8_t* lower = item + (matrix * kFusedItemRows + g) * rb1 + group * 32 + t * 8;
+                        for (int c = 0; c < 4; ++c) {
+                            const int matrix = c & 1, which = (c >> 1) && second ? gi + 1 : gi;
+                            const int group = group0 + which;
+                            op[c].lower = item + (matrix * kFusedItemRows + g) * rb1 + group * 32 + t * 8;
+                            op[c].upper = op[c].lower + 8 * rb1;
                             const uint8_t* sc = tables + ((2 * matrix) * kFusedItemRows + g) * sb1 + group * 2;
                             const uint8_t* bi = tables + ((2 * matrix + 1) * kFusedItemRows + g) * sb1 + group * 2;
-                            const uint32_t scale_lo = *reinterpret_cast<const uint16_t*>(sc);
-                            const uint32_t bias_lo = *reinterpret_cast<const uint16_t*>(bi);
-                            if (upper) {
-                                const uint32_t scale_hi = *reinterpret_cast<const uint16_t*>(sc + 8 * sb1);
-                                const uint32_t bias_hi = *reinterpret_cast<const uint16_t*>(bi + 8 * sb1);
-                                mma_group<true>(lower, lower + 8 * rb1, scale_lo, bias_lo, scale_hi, bias_hi, bx0[gi],
-                                                bx1[gi], x0[gi], x1[gi], acc[matrix]);
-                            } else {
-                                mma_group<false>(lower, nullptr, scale_lo, bias_lo, 0, 0, bx0[gi], bx1[gi], x0[gi],
-                                                 x1[gi], acc[matrix]);
+                            op[c].scale_lo = *reinterpret_cast<const uint16_t*>(sc);
+                            op[c].bias_lo = *reinterpret_cast<const uint16_t*>(bi);
+                            op[c].scale_hi = upper ? *reinterpret_cast<const uint16_t*>(sc + 8 * sb1) : 0u;
+                            op[c].bias_hi = upper ? *reinterpret_cast<const uint16_t*>(bi + 8 * sb1) : 0u;
+                            fx0[c] = (c >> 1) && second ? bx0[(gi + 1) % kFusedMmaMaxGroups1] : bx0[gi];
+                            fx1[c] = (c >> 1) && second ? bx1[(gi + 1) % kFusedMmaMaxGroups1] : bx1[gi];
+                            fs0[c] = (c >> 1) && second ? x0[(gi + 1) % kFusedMmaMaxGroups1] : x0[gi];
+                            fs1[c] = (c >> 1) && second ? x1[(gi + 1) % kFusedMmaMaxGroups1] : x1[gi];
+                            into[c] = (c >> 1) && !second ? discard : acc[matrix];
+                        }
+                        // The two chains of one matrix add into the same accumulators: fold the second
+                        // group's pair after the first by giving it its own accumulators.
+                        float later[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+                        if (second) { into[2] = later[0]; into[3] = later[1]; }
+                        if (upper) mma_groups<4, true>(op, fx0, fx1, fs0, fs1, into);
+                        else mma_groups<4, false>(op, fx0, fx1, fs0, fs1, into);
+                        if (second) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                acc[0][k] += later[0][k];
+                                acc[1][k] += later[1][k];
                             }
                         }
                     }
@@ -720,23 +764,48 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
             const int table = lay.down_rows * sb2;  // biases follow the scales
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (alive) {
-                uint4 bx0, bx1, nx0, nx1;
-                float x0, x1, y0, y1;
-                load_group_fragments<true>(column, active, group0, t, bx0, bx1, x0, x1);
-                for (int gi = 0; gi < groups; ++gi) {
-                    const int group = group0 + gi;
-                    if (gi + 1 < groups) load_group_fragments<true>(column, active, group + 1, t, nx0, nx1, y0, y1);
-                    const uint32_t scale_lo = *reinterpret_cast<const uint16_t*>(sc_lo + group * 2);
-                    const uint32_t bias_lo = *reinterpret_cast<const uint16_t*>(sc_lo + table + group * 2);
-                    if (upper) {
-                        const uint32_t scale_hi = *reinterpret_cast<const uint16_t*>(sc_hi + group * 2);
-                        const uint32_t bias_hi = *reinterpret_cast<const uint16_t*>(sc_hi + table + group * 2);
-                        mma_group<true>(lower + group * 32, upper_row + group * 32, scale_lo, bias_lo, scale_hi, bias_hi, bx0,
-                                        bx1, x0, x1, acc);
-                    } else {
-                        mma_group<false>(lower + group * 32, nullptr, scale_lo, bias_lo, 0, 0, bx0, bx1, x0, x1, acc);
+                // Four groups = four independent MMA chains per step; their activation fragments come
+                // from L2 one step ahead.  Chains past the slice's end repeat the step's first group
+                // into a discarded accumulator.
+                uint4 bx0[4], bx1[4], nx0[4], nx1[4];
+                float x0[4], x1[4], y0[4], y1[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    load_group_fragments<true>(column, active, group0 + (c < groups ? c : 0), t, bx0[c], bx1[c], x0[c], x1[c]);
+                for (int gi = 0; gi < groups; gi += 4) {
+                    if (gi + 4 < groups) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            load_group_fragments<true>(column, active, group0 + (gi + 4 + c < groups ? gi + 4 + c : gi + 4), t,
+                                                       nx0[c], nx1[c], y0[c], y1[c]);
                     }
-                    bx0 = nx0; bx1 = nx1; x0 = y0; x1 = y1;
+                    MmaOperand op[4];
+                    float part[4][4];
+                    float* into[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int group = group0 + (gi + c < groups ? gi + c : gi);
+                        op[c].lower = lower + group * 32;
+                        op[c].upper = upper_row + group * 32;
+                        op[c].scale_lo = *reinterpret_cast<const uint16_t*>(sc_lo + group * 2);
+                        op[c].bias_lo = *reinterpret_cast<const uint16_t*>(sc_lo + table + group * 2);
+                        op[c].scale_hi = upper ? *reinterpret_cast<const uint16_t*>(sc_hi + group * 2) : 0u;
+                        op[c].bias_hi = upper ? *reinterpret_cast<const uint16_t*>(sc_hi + table + group * 2) : 0u;
+                        part[c][0] = part[c][1] = part[c][2] = part[c][3] = 0.0f;
+                        into[c] = part[c];
+                    }
+                    if (upper) mma_groups<4, true>(op, bx0, bx1, x0, x1, into);
+                    else mma_groups<4, false>(op, bx0, bx1, x0, x1, into);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (gi + c < groups) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) acc[k] += part[c][k];
+                        }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        bx0[c] = nx0[c]; bx1[c] = nx1[c]; x0[c] = y0[c]; x1[c] = y1[c];
+                    }
                 }
             }
             // Hand back the items that end inside this tile.

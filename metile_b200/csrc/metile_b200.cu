@@ -271,10 +271,10 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
         params.H = H;
         params.I = I;
         const int sms = device_sm_count();
-        // Up to kFusedDefaultRows rows: the FMA kernel.  The warp-MMA kernel (to eight rows) only on request.
+        // Up to kFusedDefaultRows rows: the FMA kernel.  Four to eight rows: the warp-MMA kernel.
         const bool want_mma = (flags & MT_FLAG_MLP_FUSED_MMA) != 0;
         const bool fma = !want_mma && (flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms);
-        const bool mma = want_mma && fused_mlp_mma_applicable(params, sms);  // measured no faster than the tensor path: opt-in
+        const bool mma = !fma && (want_mma || (!flags && M > kFusedDefaultRows)) && fused_mlp_mma_applicable(params, sms);
         if (fma || mma) {
             const int fused_rc = launch_mlp_fused(params, sms, mma, static_cast<cudaStream_t>(stream));
             // A cooperative launch is refused when the whole grid cannot be resident (a GPU shared with
@@ -333,7 +333,7 @@ int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags) {
     if (sms <= 0) return 2;
     const bool want_mma = (flags & MT_FLAG_MLP_FUSED_MMA) != 0;
     if (!want_mma && (flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms)) return 1;  // null pointers count as aligned
-    return want_mma && fused_mlp_mma_applicable(params, sms) ? 1 : 2;
+    return (want_mma || (!flags && M > kFusedDefaultRows)) && fused_mlp_mma_applicable(params, sms) ? 1 : 2;
 }
 
 size_t mt_affine_mlp_static_max_bytes(void) { return kStaticHiddenBytes; }

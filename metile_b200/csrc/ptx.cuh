@@ -286,7 +286,8 @@ __device__ __forceinline__ unsigned long long atom_add_release_gpu_u64(unsigned 
 // d0, d1 = D[g][2t, 2t+1], d2, d3 = D[g+8][2t, 2t+1].
 __device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                   uint32_t b0, uint32_t b1) {
-    asm volatile(
+    // Not volatile: a pure function of its operands, so independent chains may be interleaved.
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));

@@ -242,7 +242,7 @@ def test_single_launch_mlp_up_to_four_rows(cuda_device, hidden, inter):
 
 @pytest.mark.parametrize("hidden,inter", [(2048, 8192), (1024, 2048), (1024, 1024), (2048, 4096), (512, 1536)])
 def test_single_launch_mlp_on_warp_mma_up_to_eight_rows(cuda_device, hidden, inter):
-    """The warp-MMA variant of the single-launch MLP (opt-in, up to eight rows): exact weights,
+    """The warp-MMA variant of the single-launch MLP (default for four to eight rows): exact weights,
     oracle at the MLP tolerance, rows bit-identical alone or in a batch of eight, repeatable."""
     gate, up, down = synth.mlp_weights(320, hidden, inter, cuda_device)
     triples_np = [triple_np(t) for t in (gate, up, down)]
@@ -259,8 +259,10 @@ def test_single_launch_mlp_on_warp_mma_up_to_eight_rows(cuda_device, hidden, int
         y_plain = B.mlx_affine_mlp_executor(x, *gate, *up, *down, None)(x, None)
     assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=4e-3, what=f"warp-MMA MLP {hidden}x{inter}")
     assert_within(y_plain, A.mlp(f32(x), *triples_np, None), rel=4e-3, what="warp-MMA MLP, no residual")
-    assert library.mt_affine_mlp_launches(8, hidden, inter, _lib.FLAG_MLP_FUSED_MMA) == 1
-    assert library.mt_affine_mlp_launches(8, hidden, inter, 0) == 2  # opt-in: no faster than the tensor path
+    for rows in (4, 8):
+        assert library.mt_affine_mlp_launches(rows, hidden, inter, 0) == 1
+        assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], "default dispatch is the warp-MMA kernel")
+    assert library.mt_affine_mlp_launches(9, hidden, inter, 0) == 2
     assert library.mt_affine_mlp_launches(9, hidden, inter, _lib.FLAG_MLP_FUSED_MMA) == 2
 
 
