@@ -415,19 +415,26 @@ def run_ours(args):
 
         packed = hidden * inter * (0.5 + 4 / 64)  # one projection: nibbles + bf16 scales and biases
         single_rows = [m for m in sweep if library.mt_affine_mlp_launches(m, hidden, inter, 0) == 1]
-        if single_rows:
-            x1, r1 = inputs[single_rows[0]]
-            executors_1 = [B.mlx_affine_mlp_executor(x1, *w[0], *w[1], *w[2], r1) for w in weight_sets]
+        # One launch per MLP: the CUDA-core kernel up to three rows, the warp-MMA kernel from four to eight.
+        for rows_served, label, traffic, profile in (
+                ([m for m in single_rows if m <= 3], "single-launch MLP on CUDA cores (affine_mlp_fused_kernel)", 28381952,
+                 "profiles/affine_mlp_fused_m1_llama1b.md"),
+                ([m for m in single_rows if m > 3], "single-launch MLP on mma.sync (affine_mlp_fused_mma_kernel)", 28449280,
+                 "profiles/affine_mlp_fused_mma_m8_llama1b.md")):
+            if not rows_served:
+                continue
+            m = rows_served[0] if rows_served[0] <= 3 else rows_served[-1]
+            xm, rm = inputs[m]
+            executors_m = [B.mlx_affine_mlp_executor(xm, *w[0], *w[1], *w[2], rm) for w in weight_sets]
 
-            def whole_mlp():
+            def whole_mlp(executors_m=executors_m, xm=xm, rm=rm):
                 cursor[0] = (cursor[0] + 1) % copies
-                executors_1[cursor[0]](x1, r1)
+                executors_m[cursor[0]](xm, rm)
 
             seconds = per_launch_seconds(whole_mlp, 1)
             roofline_kernels.append(entry(
-                "single-launch MLP, M=1 (affine_mlp_fused_kernel)", single_rows, seconds,
-                3 * packed + 2 * hidden * 2 + 2 * inter * 2 + hidden * 2, 28381952,
-                "profiles/affine_mlp_fused_m1_llama1b.md"))
+                f"{label}, M={m}", rows_served, seconds,
+                3 * packed + 2 * m * hidden * 2 + 2 * m * inter * 2 + m * hidden * 2, traffic, profile))
         two_kernel_rows = [m for m in sweep if m not in single_rows]
         small = [m for m in two_kernel_rows if m <= 16]
         if small:
