@@ -1,7 +1,9 @@
-// The whole INT4 affine MLP  out = down(silu(x Wg^T) * (x Wu^T)) + residual  for a single
-// activation row as ONE cooperative launch, one CTA per SM.
+// The whole INT4 affine MLP  out = down(silu(x Wg^T) * (x Wu^T)) + residual  for a handful of
+// activation rows as ONE cooperative launch, one CTA per SM.  Two kernels share the launch structure:
+// the FMA kernel described first (one to four rows, default up to three) and the warp-MMA kernel
+// further down (up to eight rows, default from four).
 //
-// Why one launch.  At one row the MLP is a pure stream of packed weights (28 MB at the
+// Why one launch.  At a few rows the MLP is a pure stream of packed weights (28 MB at the
 // Llama-3.2-1B shape: 4.4 us at the measured HBM rate), and two dependent kernels spend more time
 // starting, ramping up their loads and draining than moving those bytes.  Here a CTA streams its rows
 // of gate and up, then its rows of down, through ONE ring of shared-memory slots fed by bulk copies.
@@ -13,9 +15,9 @@
 //
 // Work split.  CTA c owns gate/up rows [c*I/grid, (c+1)*I/grid) and down rows [c*H/grid,
 // (c+1)*H/grid).  A weight row of K columns is cut into K/1024 sets of 1024 columns (32 lanes x 32
-// nibbles): warp w of the compute warps serves set w % sets and, in every ring item, the rows
-// w / sets + (warps / sets) * j.  Its activations (32 per lane, fp32 in registers) therefore never
-// change during a projection.  Per-set partial sums of a row meet in shared memory and are added
+// nibbles): warp w of the compute warps serves set w % sets and, in every ring item, the share-rows
+// w / sets + (warps / sets) * j.  Its activations (32 per lane and row, fp32 in registers) therefore
+// never change during a projection.  Per-set partial sums of a row meet in shared memory and are added
 // in set order, so the fp32 order depends on (H, I, grid) only.
 //
 // Arithmetic.  A lane turns 16 bytes of a weight row into the floats 128+q with one byte-permute
@@ -32,11 +34,12 @@
 // (32 byte-permutes, 32 FMAs, masks, scale fold, butterfly) and the SM sub-partition sustains about
 // 0.7 of them per cycle, so the MLP's 50 M weights take about 5 us of instruction issue per SM --
 // more than the 4.4 us the bytes take.  Eight compute warps with 146 registers beat sixteen with 96.
-// Also measured and dropped: a warp-level MMA variant (mma.sync m16n8k16 issues about once per 32
-// cycles per SM sub-partition), the packed fma.rn.f32x2 (the compiler moves every unpacked weight
-// into a register pair first, two extra instructions per weight), a bf16-pair unpack (same
-// instruction count as the byte-permutes), and a half-SM variant meant to let two launches overlap
-// (a cooperative launch does not start before its predecessor has drained, so nothing overlapped).
+// Each further activation row adds 32 FMAs per share, which is why the warp-MMA kernel takes over
+// at four rows.  Also measured and dropped: the packed fma.rn.f32x2 (the compiler moves every
+// unpacked weight into a register pair first, two extra instructions per weight), a bf16-pair
+// unpack (same instruction count as the byte-permutes), and a half-SM variant meant to let two
+// launches overlap (a cooperative launch does not start before its predecessor has drained, so
+// nothing overlapped).
 #pragma once
 
 #include <cstdlib>
