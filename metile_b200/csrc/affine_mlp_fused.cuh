@@ -1,7 +1,7 @@
 // The whole INT4 affine MLP  out = down(silu(x Wg^T) * (x Wu^T)) + residual  for a handful of
 // activation rows as ONE cooperative launch, one CTA per SM.  Two kernels share the launch structure:
-// the FMA kernel described first (one to four rows, default up to three) and the warp-MMA kernel
-// further down (up to eight rows, default from four).
+// the FMA kernel described first (one to four rows, default up to two) and the warp-MMA kernel
+// further down (up to eight rows, default from three).
 //
 // Why one launch.  At a few rows the MLP is a pure stream of packed weights (28 MB at the
 // Llama-3.2-1B shape: 4.4 us at the measured HBM rate), and two dependent kernels spend more time
@@ -35,12 +35,14 @@
 // 0.7 of them per cycle, so the MLP's 50 M weights take about 5 us of instruction issue per SM --
 // more than the 4.4 us the bytes take.  Eight compute warps with 146 registers beat sixteen with 96.
 // Each further activation row adds 32 FMAs per share, which is why the warp-MMA kernel takes over
-// at four rows.  Also measured and dropped: the packed fma.rn.f32x2 (the compiler moves every
+// at three rows.  Also measured and dropped: the packed fma.rn.f32x2 (the compiler moves every
 // unpacked weight into a register pair first, two extra instructions per weight), a bf16-pair
 // unpack (same instruction count as the byte-permutes), and a half-SM variant meant to let two
 // launches overlap (a cooperative launch does not start before its predecessor has drained, so
 // nothing overlapped).
 #pragma once
+
+#include <cuda.h>
 
 #include <cstdlib>
 
@@ -59,8 +61,9 @@ constexpr int kFusedComputeWarps = MT_FUSED_WARPS;
 constexpr int kFusedComputeThreads = kFusedComputeWarps * 32;
 constexpr int kFusedThreads = kFusedComputeThreads + 32;  // + the producer warp
 constexpr int kFusedMaxRows = 4;       // activation rows (each lane keeps 32 fp32 activations per row in registers)
-constexpr int kFusedDefaultRows = 3;   // rows served by default (measured faster than the two-kernel path up to
-                                       // three rows); four rows only when asked with MT_FLAG_MLP_FUSED
+constexpr int kFusedDefaultRows = 2;   // rows the FMA kernel serves by default (measured: 16.1 / 19.9 / 22.4 us at
+                                       // 1 / 2 / 3 rows against 20.1 us for the warp-MMA kernel); three and four
+                                       // rows only when asked with MT_FLAG_MLP_FUSED
 constexpr int kFusedMaxSlots = 12;
 constexpr int kFusedItemRows = MT_FUSED_ITEM_ROWS;  // gate/up rows per ring item
 constexpr int kFusedSmemBudget = 226 * 1024;  // one CTA per SM
@@ -77,6 +80,8 @@ enum FusedWaitCode : unsigned int {
 __device__ unsigned long long g_fused_barrier[kFusedBarrierSlots];
 
 struct FusedMlpParams {
+    CUtensorMap gate_map;      // warp-MMA kernel only: gate_w / up_w as [I, H/8] uint32 tensors, boxes of
+    CUtensorMap up_map;        // 32 words x 16 rows with the 128-byte swizzle
     const uint16_t* x;         // [1, H] bf16
     const uint32_t* gate_w;    // [I, H/8]
     const uint32_t* up_w;      // [I, H/8]
@@ -268,6 +273,11 @@ __device__ __forceinline__ void fused_grid_barrier(unsigned long long* slot, int
 
 // The producer warp of both kernel variants: streams the CTA's items through the ring.  Weights do
 // not depend on the preceding kernel, so nothing here waits for it.  Lanes 0..5 each issue one copy.
+// kTiled: the gate|up rows of an item arrive as 128-byte-wide tensor-map boxes (32 words x 16 rows, 128-byte
+// swizzle; layout [matrix][H/256 column blocks][16 rows][128 B]) instead of dense rows -- what the warp-MMA
+// kernel's fragment loads need to stay free of bank conflicts.  A box is always 16 rows: rows past the
+// CTA's share (or past the tensor, zero-filled) are simply not used.
+template <bool kTiled>
 __device__ __forceinline__ void fused_producer(const FusedMlpParams& p, const FusedMlpLayout& lay, uint8_t* ring,
                                                uint64_t* full_bar, uint64_t* empty_bar, volatile int* abort_flag,
                                                int lane, int row1, int n1, int row2, int n2) {
@@ -284,15 +294,33 @@ __device__ __forceinline__ void fused_producer(const FusedMlpParams& p, const Fu
         if (it < items1) {
             const int rows = min(kFusedItemRows, n1 - kFusedItemRows * it);
             const size_t r0 = (size_t)(row1 + kFusedItemRows * it);
-            if (lane == 0) ptx::mbar_expect_tx(&full_bar[slot], (uint32_t)rows * (uint32_t)(2 * rb1 + 4 * sb1));
-            __syncwarp();
-            if (lane < 2) {
-                const uint32_t* src = (lane ? p.up_w : p.gate_w) + r0 * (size_t)(H >> 3);
-                ptx::bulk_load(dst + lane * kFusedItemRows * rb1, src, (uint32_t)rows * rb1, &full_bar[slot]);
-            } else if (lane < 6) {
-                const uint16_t* base = lane == 2 ? p.gate_s : lane == 3 ? p.gate_b : lane == 4 ? p.up_s : p.up_b;
-                ptx::bulk_load(dst + 2 * kFusedItemRows * rb1 + (lane - 2) * kFusedItemRows * sb1,
-                               base + r0 * (size_t)(H >> 6), (uint32_t)rows * sb1, &full_bar[slot]);
+            if constexpr (kTiled) {
+                const int blocks = H >> 8;  // 256 columns = 128 packed bytes per box
+                if (lane == 0)
+                    ptx::mbar_expect_tx(&full_bar[slot], (uint32_t)(2 * kFusedItemRows * rb1) + (uint32_t)rows * (uint32_t)(4 * sb1));
+                __syncwarp();
+                for (int box = lane; box < 2 * blocks; box += 32) {
+                    const int matrix = box / blocks, block = box - matrix * blocks;
+                    ptx::tma_load_2d(dst + (size_t)box * (kFusedItemRows * 128), matrix ? &p.up_map : &p.gate_map, block * 32,
+                                     (int)r0, &full_bar[slot]);
+                }
+                if (lane >= 28) {
+                    const int which = lane - 28;
+                    const uint16_t* base = which == 0 ? p.gate_s : which == 1 ? p.gate_b : which == 2 ? p.up_s : p.up_b;
+                    ptx::bulk_load(dst + 2 * kFusedItemRows * rb1 + which * kFusedItemRows * sb1,
+                                   base + r0 * (size_t)(H >> 6), (uint32_t)rows * sb1, &full_bar[slot]);
+                }
+            } else {
+                if (lane == 0) ptx::mbar_expect_tx(&full_bar[slot], (uint32_t)rows * (uint32_t)(2 * rb1 + 4 * sb1));
+                __syncwarp();
+                if (lane < 2) {
+                    const uint32_t* src = (lane ? p.up_w : p.gate_w) + r0 * (size_t)(H >> 3);
+                    ptx::bulk_load(dst + lane * kFusedItemRows * rb1, src, (uint32_t)rows * rb1, &full_bar[slot]);
+                } else if (lane < 6) {
+                    const uint16_t* base = lane == 2 ? p.gate_s : lane == 3 ? p.gate_b : lane == 4 ? p.up_s : p.up_b;
+                    ptx::bulk_load(dst + 2 * kFusedItemRows * rb1 + (lane - 2) * kFusedItemRows * sb1,
+                                   base + r0 * (size_t)(H >> 6), (uint32_t)rows * sb1, &full_bar[slot]);
+                }
             }
         } else {
             const int j = it - items1;
@@ -351,7 +379,7 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     ptx::griddep_launch_dependents();
 
     if (warp == kFusedComputeWarps) {
-        fused_producer(p, lay, ring, full_bar, empty_bar, abort_flag, lane, row1, n1, row2, n2);
+        fused_producer<false>(p, lay, ring, full_bar, empty_bar, abort_flag, lane, row1, n1, row2, n2);
         return;
     }
 
@@ -501,8 +529,12 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
 // about once per 32 cycles per SM sub-partition on this part, which bounds the kernel near the FMA
 // kernel's one-row time, independent of the row count.  The four MMAs of a group are a dependent chain,
 // so four (block, group) pairs are issued round-robin; with one chain at a time the kernel took 25 us.
-// Measured at the Llama-3.2-1B shape: 21.5-22.5 us for 1-8 rows against 25.4-25.8 us on the two-kernel
-// tensor-core path, so it is the default for four to eight rows.
+// The fragment loads are 64 bits per lane from four weight rows at a time; in a dense row layout those
+// rows share their banks (4-way conflicts, 1.5 M extra wavefronts per launch), so the gate|up rows arrive
+// as 128-byte-swizzled tensor-map boxes and fragment row g is given weight row 2 (g % 4) + g / 4, which
+// makes the four rows' swizzles differ.  Measured at the Llama-3.2-1B shape: 19.9-20.3 us for 1-8 rows
+// (22 us with dense rows) against 25.4-25.9 us on the two-kernel tensor-core path, so it is the default
+// for three to eight rows.
 //
 // Same producer, ring and grid barrier.  The K range is cut into one slice per compute warp; every
 // warp walks all rows of an item for its slice; the warps' partial 16 x 8 tiles meet in shared memory
@@ -603,7 +635,8 @@ __device__ __forceinline__ void mma_groups(const MmaOperand (&op)[kN], const uin
 __global__ void __launch_bounds__(kFusedThreads, 1)
 affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
     extern __shared__ uint8_t fused_smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fused_smem_raw) + 127) & ~(uintptr_t)127);
+    // 1024-byte alignment: the swizzle pattern of the tensor-map boxes repeats every 1024 bytes.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fused_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int grid = gridDim.x, cta = blockIdx.x;
     const int M = p.M, H = p.H, I = p.I;
     const FusedMlpLayout lay = fused_mlp_layout(kFusedMmaMaxRows, H, I, grid);
@@ -635,7 +668,11 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
     __syncthreads();
     ptx::griddep_launch_dependents();
     if (warp == kFusedComputeWarps) {
-        fused_producer(p, lay, ring, full_bar, empty_bar, abort_flag, lane, row1, n1, row2, n2);
+        if (lane == 0) {
+            ptx::prefetch_tensor_map(&p.gate_map);
+            ptx::prefetch_tensor_map(&p.up_map);
+        }
+        fused_producer<true>(p, lay, ring, full_bar, empty_bar, abort_flag, lane, row1, n1, row2, n2);
         return;
     }
 
@@ -652,6 +689,9 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
         // ------------------------------------------------------------------ gate | up
         const int groups = (H >> 6) / kFusedComputeWarps;  // quantisation groups in this warp's K slice (<= 4)
         const int group0 = warp * groups;
+        // Fragment row g carries weight row 2 (g % 4) + g / 4 of each 8-row half: the four rows a half-warp
+        // loads at once then differ in their swizzle by 0, 2, 4, 6 and hit disjoint banks.
+        const int wrow = ((g & 3) << 1) | (g >> 2);
         uint4 bx0[kFusedMmaMaxGroups1], bx1[kFusedMmaMaxGroups1];
         float x0[kFusedMmaMaxGroups1], x1[kFusedMmaMaxGroups1];
 #pragma unroll
@@ -682,10 +722,14 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
                         for (int c = 0; c < 4; ++c) {
                             const int matrix = c & 1, which = (c >> 1) && second ? gi + 1 : gi;
                             const int group = group0 + which;
-                            op[c].lower = item + (matrix * kFusedItemRows + g) * rb1 + group * 32 + t * 8;
-                            op[c].upper = op[c].lower + 8 * rb1;
-                            const uint8_t* sc = tables + ((2 * matrix) * kFusedItemRows + g) * sb1 + group * 2;
-                            const uint8_t* bi = tables + ((2 * matrix + 1) * kFusedItemRows + g) * sb1 + group * 2;
+                            // Box (matrix, group / 4), row `wrow`, 16-byte chunk (group % 4) * 2 + t / 2 XOR-swizzled
+                            // by the row; rows wrow and wrow + 8 share the swizzle.
+                            const int chunk = (((group & 3) << 1) | (t >> 1)) ^ (wrow & 7);
+                            op[c].lower = item + (size_t)((matrix * (H >> 8) + (group >> 2)) * kFusedItemRows + wrow) * 128 +
+                                          (chunk << 4) + (t & 1) * 8;
+                            op[c].upper = op[c].lower + 8 * 128;
+                            const uint8_t* sc = tables + ((2 * matrix) * kFusedItemRows + wrow) * sb1 + group * 2;
+                            const uint8_t* bi = tables + ((2 * matrix + 1) * kFusedItemRows + wrow) * sb1 + group * 2;
                             op[c].scale_lo = *reinterpret_cast<const uint16_t*>(sc);
                             op[c].bias_lo = *reinterpret_cast<const uint16_t*>(bi);
                             op[c].scale_hi = upper ? *reinterpret_cast<const uint16_t*>(sc + 8 * sb1) : 0u;
@@ -721,8 +765,8 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
 #pragma unroll
             for (int matrix = 0; matrix < 2; ++matrix) {
                 float* tile = scratch + (size_t)((warp * 2 + matrix) * 16) * 8;
-                *reinterpret_cast<float2*>(tile + g * 8 + 2 * t) = make_float2(acc[matrix][0], acc[matrix][1]);
-                *reinterpret_cast<float2*>(tile + (g + 8) * 8 + 2 * t) = make_float2(acc[matrix][2], acc[matrix][3]);
+                *reinterpret_cast<float2*>(tile + wrow * 8 + 2 * t) = make_float2(acc[matrix][0], acc[matrix][1]);
+                *reinterpret_cast<float2*>(tile + (wrow + 8) * 8 + 2 * t) = make_float2(acc[matrix][2], acc[matrix][3]);
             }
             fused_compute_sync();
             for (int idx = threadIdx.x; idx < rows_here * M; idx += kFusedComputeThreads) {
@@ -850,7 +894,8 @@ inline bool fused_mlp_mma_applicable(const FusedMlpParams& p, int sm_count) {
     const FusedMlpLayout lay = fused_mlp_layout(kFusedMmaMaxRows, p.H, p.I, sm_count);
     if (lay.slots < 2 || lay.down_rows < 8 || lay.down_rows % 8) return false;
     if (16 * p.M > kFusedComputeThreads) return false;
-    if (lay.total + 128 > kFusedSmemBudget) return false;
+    if (p.H % 256 || lay.item_bytes % 1024) return false;  // whole tensor-map boxes, swizzle-aligned items
+    if (lay.total + 1024 > kFusedSmemBudget) return false;
     const void* pointers[] = {p.x, p.gate_w, p.up_w, p.down_w, p.gate_s, p.gate_b, p.up_s, p.up_b, p.down_s, p.down_b,
                               p.hidden};
     for (const void* ptr : pointers)
@@ -942,7 +987,10 @@ inline int launch_mlp_fused(FusedMlpParams params, int sm_count, bool mma, cudaS
     }
     params.barrier = slots[device] + (__atomic_fetch_add(&launches, 1u, __ATOMIC_RELAXED) % kFusedBarrierSlots);
     if (mma) {
-        const int smem = fused_mlp_layout(kFusedMmaMaxRows, params.H, params.I, sm_count).total + 128;
+        if (!encode_weight_map(&params.gate_map, params.gate_w, params.H, params.I, kFusedItemRows) ||
+            !encode_weight_map(&params.up_map, params.up_w, params.H, params.I, kFusedItemRows))
+            return MT_ERR_LAUNCH;
+        const int smem = fused_mlp_layout(kFusedMmaMaxRows, params.H, params.I, sm_count).total + 1024;
         return launch_mlp_fused_kernel<0>(affine_mlp_fused_mma_kernel, smem, params, sm_count, device, stream);
     }
     switch (params.M) {

@@ -577,12 +577,12 @@ inline EncodeTiledFn encode_tiled_fn() {
 
 // Packed weights as a 2-D uint32 tensor [N, K/8]; box = 32 words (128 B, four k-blocks) x 128 rows,
 // 128-byte swizzle so that a thread reading "its" row's 32 bytes hits distinct banks.
-inline bool encode_weight_map(CUtensorMap* map, const void* base, int K, int N) {
+inline bool encode_weight_map(CUtensorMap* map, const void* base, int K, int N, int box_rows = kUmmaTileRows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K / 8, (cuuint64_t)N};
     cuuint64_t strides[1] = {(cuuint64_t)K / 2};
-    cuuint32_t box[2] = {32, (cuuint32_t)kUmmaTileRows};
+    cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
     cuuint32_t elem_strides[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -4,8 +4,8 @@
 
 #include "add_rmsnorm.cuh"
 #include "affine_gemv.cuh"
-#include "affine_mlp_fused.cuh"
 #include "affine_umma.cuh"
+#include "affine_mlp_fused.cuh"
 #include "affine_umma_scaled.cuh"
 #include "common.cuh"
 #include "dense_rows.cuh"
@@ -271,7 +271,7 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
         params.H = H;
         params.I = I;
         const int sms = device_sm_count();
-        // Up to kFusedDefaultRows rows: the FMA kernel.  Four to eight rows: the warp-MMA kernel.
+        // Up to kFusedDefaultRows rows: the FMA kernel.  Above, to eight rows: the warp-MMA kernel.
         const bool want_mma = (flags & MT_FLAG_MLP_FUSED_MMA) != 0;
         const bool fma = !want_mma && (flags || M <= kFusedDefaultRows) && fused_mlp_applicable(params, sms);
         const bool mma = !fma && (want_mma || (!flags && M > kFusedDefaultRows)) && fused_mlp_mma_applicable(params, sms);
