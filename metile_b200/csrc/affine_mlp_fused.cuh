@@ -582,6 +582,21 @@ __device__ __forceinline__ void load_group_fragments(const uint16_t* column, boo
 // kN independent (16-row block, quantisation group) pairs at once: rows g (lower) and g+8 (upper) of
 // each fragment.  The four MMAs of a pair form a dependent chain (they accumulate one group's partial
 // sums), so the pairs' MMAs are issued round-robin to keep the tensor pipe fed.
+// Four consecutive bf16 table entries (scales or biases of groups group..group+3 of one row) as one
+// 64-bit load when they are 8-byte aligned, else entry by entry; entries past `count` are not read.
+__device__ __forceinline__ uint2 load_four_entries(const uint8_t* row, int group, int count) {
+    if (((group & 3) == 0) && count >= 4) return *reinterpret_cast<const uint2*>(row + group * 2);
+    uint32_t e[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (i < count) e[i] = *reinterpret_cast<const uint16_t*>(row + (group + i) * 2);
+    return make_uint2(e[0] | (e[1] << 16), e[2] | (e[3] << 16));
+}
+__device__ __forceinline__ uint32_t entry_of(uint2 four, int i) {
+    const uint32_t word = i < 2 ? four.x : four.y;
+    return (i & 1) ? word >> 16 : word & 0xFFFFu;
+}
+
 struct MmaOperand {
     const uint8_t* lower;   // this lane's 8 packed bytes of row g for the group
     const uint8_t* upper;   // ... of row g+8 (ignored without kUpper)
@@ -707,6 +722,19 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
             const bool upper = rows_here > 8;
             float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
             if (alive) {
+                // This warp's scales and biases of the item: rows wrow and wrow + 8, gate and up, four groups each.
+                uint2 sc4[2][2], bi4[2][2];  // [matrix][lower / upper]
+#pragma unroll
+                for (int matrix = 0; matrix < 2; ++matrix)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int row = wrow + 8 * half;
+                        const bool present = half == 0 || upper;
+                        sc4[matrix][half] = present ? load_four_entries(tables + ((2 * matrix) * kFusedItemRows + row) * sb1, group0, groups)
+                                                    : make_uint2(0, 0);
+                        bi4[matrix][half] = present ? load_four_entries(tables + ((2 * matrix + 1) * kFusedItemRows + row) * sb1, group0, groups)
+                                                    : make_uint2(0, 0);
+                    }
                 // Two groups x (gate, up) = four independent MMA chains per step.  A second group past
                 // the slice's end repeats the first one into a discarded accumulator.
 #pragma unroll
@@ -728,12 +756,10 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
                             op[c].lower = item + (size_t)((matrix * (H >> 8) + (group >> 2)) * kFusedItemRows + wrow) * 128 +
                                           (chunk << 4) + (t & 1) * 8;
                             op[c].upper = op[c].lower + 8 * 128;
-                            const uint8_t* sc = tables + ((2 * matrix) * kFusedItemRows + wrow) * sb1 + group * 2;
-                            const uint8_t* bi = tables + ((2 * matrix + 1) * kFusedItemRows + wrow) * sb1 + group * 2;
-                            op[c].scale_lo = *reinterpret_cast<const uint16_t*>(sc);
-                            op[c].bias_lo = *reinterpret_cast<const uint16_t*>(bi);
-                            op[c].scale_hi = upper ? *reinterpret_cast<const uint16_t*>(sc + 8 * sb1) : 0u;
-                            op[c].bias_hi = upper ? *reinterpret_cast<const uint16_t*>(bi + 8 * sb1) : 0u;
+                            op[c].scale_lo = entry_of(sc4[matrix][0], which);
+                            op[c].bias_lo = entry_of(bi4[matrix][0], which);
+                            op[c].scale_hi = entry_of(sc4[matrix][1], which);
+                            op[c].bias_hi = entry_of(bi4[matrix][1], which);
                             fx0[c] = (c >> 1) && second ? bx0[(gi + 1) % kFusedMmaMaxGroups1] : bx0[gi];
                             fx1[c] = (c >> 1) && second ? bx1[(gi + 1) % kFusedMmaMaxGroups1] : bx1[gi];
                             fs0[c] = (c >> 1) && second ? x0[(gi + 1) % kFusedMmaMaxGroups1] : x0[gi];
@@ -829,15 +855,21 @@ affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
                     MmaOperand op[4];
                     float part[4][4];
                     float* into[4];
+                    const int step_groups = min(4, groups - gi);
+                    const uint2 s_lo4 = load_four_entries(sc_lo, group0 + gi, step_groups);
+                    const uint2 b_lo4 = load_four_entries(sc_lo + table, group0 + gi, step_groups);
+                    const uint2 s_hi4 = upper ? load_four_entries(sc_hi, group0 + gi, step_groups) : make_uint2(0, 0);
+                    const uint2 b_hi4 = upper ? load_four_entries(sc_hi + table, group0 + gi, step_groups) : make_uint2(0, 0);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        const int group = group0 + (gi + c < groups ? gi + c : gi);
+                        const int within = gi + c < groups ? c : 0;
+                        const int group = group0 + gi + within;
                         op[c].lower = lower + group * 32;
                         op[c].upper = upper_row + group * 32;
-                        op[c].scale_lo = *reinterpret_cast<const uint16_t*>(sc_lo + group * 2);
-                        op[c].bias_lo = *reinterpret_cast<const uint16_t*>(sc_lo + table + group * 2);
-                        op[c].scale_hi = upper ? *reinterpret_cast<const uint16_t*>(sc_hi + group * 2) : 0u;
-                        op[c].bias_hi = upper ? *reinterpret_cast<const uint16_t*>(sc_hi + table + group * 2) : 0u;
+                        op[c].scale_lo = entry_of(s_lo4, within);
+                        op[c].bias_lo = entry_of(b_lo4, within);
+                        op[c].scale_hi = entry_of(s_hi4, within);
+                        op[c].bias_hi = entry_of(b_hi4, within);
                         part[c][0] = part[c][1] = part[c][2] = part[c][3] = 0.0f;
                         into[c] = part[c];
                     }
