@@ -415,15 +415,15 @@ def run_ours(args):
 
         packed = hidden * inter * (0.5 + 4 / 64)  # one projection: nibbles + bf16 scales and biases
         single_rows = [m for m in sweep if library.mt_affine_mlp_launches(m, hidden, inter, 0) == 1]
-        # One launch per MLP: the CUDA-core kernel up to three rows, the warp-MMA kernel from four to eight.
+        # One launch per MLP: the CUDA-core kernel for one row, the warp-MMA kernel from two to eight.
         for rows_served, label, traffic, profile in (
-                ([m for m in single_rows if m <= 3], "single-launch MLP on CUDA cores (affine_mlp_fused_kernel)", 28381952,
+                ([m for m in single_rows if m <= 1], "single-launch MLP on CUDA cores (affine_mlp_fused_kernel)", 28381952,
                  "profiles/affine_mlp_fused_m1_llama1b.md"),
-                ([m for m in single_rows if m > 3], "single-launch MLP on mma.sync (affine_mlp_fused_mma_kernel)", 28449280,
+                ([m for m in single_rows if m > 1], "single-launch MLP on mma.sync (affine_mlp_fused_mma_kernel)", 28454912,
                  "profiles/affine_mlp_fused_mma_m8_llama1b.md")):
             if not rows_served:
                 continue
-            m = rows_served[0] if rows_served[0] <= 3 else rows_served[-1]
+            m = rows_served[0] if rows_served[0] <= 1 else rows_served[-1]
             xm, rm = inputs[m]
             executors_m = [B.mlx_affine_mlp_executor(xm, *w[0], *w[1], *w[2], rm) for w in weight_sets]
 

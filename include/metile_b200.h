@@ -31,11 +31,11 @@
  *   MT_FLAG_GELU (16)        mt_dense_act: x/(1+exp(-1.702x)) instead of SiLU
  *   MT_FLAG_MLP_FUSED (32)   mt_affine_mlp: insist on the single-launch kernel (M <= 4, H and I in
  *                            {1024, 2048, 4096, 8192}); -1 when it does not apply.  With flags = 0
- *                            mt_affine_mlp uses it for M <= 2 whenever it applies, and takes the
+ *                            mt_affine_mlp uses it for M = 1 whenever it applies, and takes the
  *                            two-kernel path if the driver refuses the cooperative launch.
  *   MT_FLAG_MLP_FUSED_MMA (128) mt_affine_mlp: insist on the warp-MMA variant of the single-launch
  *                            kernel (M <= 8, H in {512, 1024, 1536, 2048}, I a multiple of 512); -1
- *                            when it does not apply.  With flags = 0 it serves M = 3 ... 8.
+ *                            when it does not apply.  With flags = 0 it serves M = 2 ... 8.
  */
 #ifndef METILE_B200_H
 #define METILE_B200_H
@@ -121,8 +121,8 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
                        unsigned int flags, void* stream);
 
 /* How many kernels mt_affine_mlp queues for this problem on the current device with 16-byte
- * aligned operands: 1 when a single-launch kernel serves it (up to two rows on CUDA cores, four with
- * MT_FLAG_MLP_FUSED, H and I in {1024, 2048, 4096, 8192}; three to eight rows on mma.sync, H <= 2048),
+ * aligned operands: 1 when a single-launch kernel serves it (one row on CUDA cores, up to four with
+ * MT_FLAG_MLP_FUSED, H and I in {1024, 2048, 4096, 8192}; two to eight rows on mma.sync, H <= 2048),
  * else 2 (gate|up
  * SwiGLU, then down); 0 for M <= 0.  No counterpart in the reference project; used for launch
  * accounting. */

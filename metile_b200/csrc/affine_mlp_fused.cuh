@@ -1,7 +1,7 @@
 // The whole INT4 affine MLP  out = down(silu(x Wg^T) * (x Wu^T)) + residual  for a handful of
 // activation rows as ONE cooperative launch, one CTA per SM.  Two kernels share the launch structure:
-// the FMA kernel described first (one to four rows, default up to two) and the warp-MMA kernel
-// further down (up to eight rows, default from three).
+// the FMA kernel described first (one to four rows, default for one) and the warp-MMA kernel
+// further down (up to eight rows, default from two).
 //
 // Why one launch.  At a few rows the MLP is a pure stream of packed weights (28 MB at the
 // Llama-3.2-1B shape: 4.4 us at the measured HBM rate), and two dependent kernels spend more time
@@ -35,7 +35,7 @@
 // 0.7 of them per cycle, so the MLP's 50 M weights take about 5 us of instruction issue per SM --
 // more than the 4.4 us the bytes take.  Eight compute warps with 146 registers beat sixteen with 96.
 // Each further activation row adds 32 FMAs per share, which is why the warp-MMA kernel takes over
-// at three rows.  Also measured and dropped: the packed fma.rn.f32x2 (the compiler moves every
+// at two rows.  Also measured and dropped: the packed fma.rn.f32x2 (the compiler moves every
 // unpacked weight into a register pair first, two extra instructions per weight), a bf16-pair
 // unpack (same instruction count as the byte-permutes), and a half-SM variant meant to let two
 // launches overlap (a cooperative launch does not start before its predecessor has drained, so
@@ -61,8 +61,8 @@ constexpr int kFusedComputeWarps = MT_FUSED_WARPS;
 constexpr int kFusedComputeThreads = kFusedComputeWarps * 32;
 constexpr int kFusedThreads = kFusedComputeThreads + 32;  // + the producer warp
 constexpr int kFusedMaxRows = 4;       // activation rows (each lane keeps 32 fp32 activations per row in registers)
-constexpr int kFusedDefaultRows = 2;   // rows the FMA kernel serves by default (measured: 16.1 / 19.9 / 22.4 us at
-                                       // 1 / 2 / 3 rows against 20.1 us for the warp-MMA kernel); three and four
+constexpr int kFusedDefaultRows = 1;   // rows the FMA kernel serves by default (measured: 16.2 / 20.1 / 22.4 us at
+                                       // 1 / 2 / 3 rows against 19.3 us for the warp-MMA kernel); two to four
                                        // rows only when asked with MT_FLAG_MLP_FUSED
 constexpr int kFusedMaxSlots = 12;
 constexpr int kFusedItemRows = MT_FUSED_ITEM_ROWS;  // gate/up rows per ring item
@@ -532,9 +532,10 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
 // The fragment loads are 64 bits per lane from four weight rows at a time; in a dense row layout those
 // rows share their banks (4-way conflicts, 1.5 M extra wavefronts per launch), so the gate|up rows arrive
 // as 128-byte-swizzled tensor-map boxes and fragment row g is given weight row 2 (g % 4) + g / 4, which
-// makes the four rows' swizzles differ.  Measured at the Llama-3.2-1B shape: 19.9-20.3 us for 1-8 rows
-// (22 us with dense rows) against 25.4-25.9 us on the two-kernel tensor-core path, so it is the default
-// for three to eight rows.
+// makes the four rows' swizzles differ; scales and biases are read four groups per load (their rows lie
+// 64 or 256 bytes apart, again in the same banks).  Measured at the Llama-3.2-1B shape: 19.2-19.5 us for
+// 1-8 rows (22 us with dense rows, 20.3 us before the wide table loads) against 25.4-25.9 us on the
+// two-kernel tensor-core path, so it is the default for two to eight rows.
 //
 // Same producer, ring and grid barrier.  The K range is cut into one slice per compute warp; every
 // warp walks all rows of an item for its slice; the warps' partial 16 x 8 tiles meet in shared memory

@@ -209,7 +209,7 @@ def test_config1_fused_mlp_llama_1b(cuda_device, rows):
 def test_single_launch_mlp_up_to_four_rows(cuda_device, hidden, inter):
     """The single-launch MLP kernel (one to four activation rows): exact weights, compared with the
     oracle at the MLP tolerance; a row's bits do not depend on how many rows share the launch; the
-    default dispatch uses it up to two rows; repeated back-to-back launches (programmatic
+    default dispatch uses it for one row; repeated back-to-back launches (programmatic
     dependent launch between them) give the same bits."""
     gate, up, down = synth.mlp_weights(300, hidden, inter, cuda_device)
     triples_np = [triple_np(t) for t in (gate, up, down)]
@@ -226,9 +226,8 @@ def test_single_launch_mlp_up_to_four_rows(cuda_device, hidden, inter):
     assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=4e-3, what=f"single-launch MLP {hidden}x{inter}")
     for other in again:
         assert_bit_equal(other, full, "repeat launch")
-    for rows in (1, 2):
-        assert library.mt_affine_mlp_launches(rows, hidden, inter, 0) == 1
-        assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], "default dispatch is the single-launch kernel")
+    assert library.mt_affine_mlp_launches(1, hidden, inter, 0) == 1
+    assert_bit_equal(execute(x[:1], res[:1]), full[:1], "default dispatch at one row is this kernel")
     assert library.mt_affine_mlp_launches(4, hidden, inter, _lib.FLAG_MLP_FUSED) == 1
     # Without a residual, and against the two-kernel path (different fp32 order, same tolerance).
     no_residual = B.mlx_affine_mlp_executor(x, *gate, *up, *down, None)
@@ -242,7 +241,7 @@ def test_single_launch_mlp_up_to_four_rows(cuda_device, hidden, inter):
 
 @pytest.mark.parametrize("hidden,inter", [(2048, 8192), (1024, 2048), (1024, 1024), (2048, 4096), (512, 1536)])
 def test_single_launch_mlp_on_warp_mma_up_to_eight_rows(cuda_device, hidden, inter):
-    """The warp-MMA variant of the single-launch MLP (default for three to eight rows): exact weights,
+    """The warp-MMA variant of the single-launch MLP (default for two to eight rows): exact weights,
     oracle at the MLP tolerance, rows bit-identical alone or in a batch of eight, repeatable."""
     gate, up, down = synth.mlp_weights(320, hidden, inter, cuda_device)
     triples_np = [triple_np(t) for t in (gate, up, down)]
@@ -259,7 +258,7 @@ def test_single_launch_mlp_on_warp_mma_up_to_eight_rows(cuda_device, hidden, int
         y_plain = B.mlx_affine_mlp_executor(x, *gate, *up, *down, None)(x, None)
     assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=4e-3, what=f"warp-MMA MLP {hidden}x{inter}")
     assert_within(y_plain, A.mlp(f32(x), *triples_np, None), rel=4e-3, what="warp-MMA MLP, no residual")
-    for rows in (3, 4, 8):
+    for rows in (2, 3, 4, 8):
         assert library.mt_affine_mlp_launches(rows, hidden, inter, 0) == 1
         assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], "default dispatch is the warp-MMA kernel")
     assert library.mt_affine_mlp_launches(9, hidden, inter, 0) == 2
