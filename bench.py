@@ -419,7 +419,7 @@ def run_ours(args):
         for rows_served, label, traffic, profile in (
                 ([m for m in single_rows if m <= 1], "single-launch MLP on CUDA cores (affine_mlp_fused_kernel)", 28381952,
                  "profiles/affine_mlp_fused_m1_llama1b.md"),
-                ([m for m in single_rows if m > 1], "single-launch MLP on mma.sync (affine_mlp_fused_mma_kernel)", 28454912,
+                ([m for m in single_rows if m > 1], "single-launch MLP on mma.sync (affine_mlp_fused_mma_kernel)", 28458496,
                  "profiles/affine_mlp_fused_mma_m8_llama1b.md")):
             if not rows_served:
                 continue
