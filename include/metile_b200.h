@@ -55,6 +55,7 @@ extern "C" {
 #define MT_FLAG_MLP_FUSED 0x20u
 #define MT_FLAG_HOST_PAIR 0x40u
 #define MT_FLAG_MLP_FUSED_MMA 0x80u
+#define MT_FLAG_STREAM 0x100u
 
 /* Library version (major*10000 + minor*100 + patch). */
 int mt_version(void);

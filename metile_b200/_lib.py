@@ -20,6 +20,7 @@ FLAG_MLP_FUSED = 0x20
 FLAG_HOST_PAIR = 0x40
 FLAG_MLP_FUSED_MMA = 0x80
 FLAG_GELU = 0x10
+FLAG_STREAM = 0x100
 
 _VALUE_ERRORS = {-1, -2, -3, -6, -7}
 

@@ -68,7 +68,7 @@ def force_kernel(name):
     single-launch MLP on CUDA cores / on mma.sync; projections called on their own are unaffected) or None."""
     table = {None: 0, "gemv": _lib.FLAG_FORCE_GEMV, "umma": _lib.FLAG_FORCE_UMMA,
              "umma_smem": _lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A,
-             "umma_scaled": _lib.FLAG_UMMA_SCALED, "mlp_fused": _lib.FLAG_MLP_FUSED,
+             "umma_scaled": _lib.FLAG_UMMA_SCALED, "stream": _lib.FLAG_STREAM, "mlp_fused": _lib.FLAG_MLP_FUSED,
              "mlp_fused_mma": _lib.FLAG_MLP_FUSED_MMA}
     if name not in table:
         raise ValueError(f"unknown kernel family {name!r}")
@@ -83,6 +83,8 @@ def force_kernel(name):
 def _algorithm(rows, flags):
     if flags & _lib.FLAG_FORCE_GEMV:
         return "gemv"
+    if flags & _lib.FLAG_STREAM:
+        return "stream"
     if flags & _lib.FLAG_UMMA_SCALED:
         return "umma_scaled"
     if flags & (_lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A):

@@ -128,6 +128,108 @@ def _surfaces(model):
     return tuple(found)
 
 
+@dataclass
+class _Outcome:
+    """One candidate feature set applied to the model: the live patch handle when it was accepted."""
+
+    selected: tuple
+    handle: object = None
+    difference: float | None = None
+    ran: bool = True
+
+    @property
+    def accepted(self):
+        return self.handle is not None
+
+    def release(self):
+        if self.handle is not None:
+            self.handle.__exit__(None, None, None)
+            self.handle = None
+
+
+class _Verifier:
+    """Applies feature sets to one model and judges each against the unpatched logits.
+
+    The unpatched logits are taken once, at construction.  When the model cannot even run unpatched,
+    verification is switched off and the reason is kept for the report (the reference does the same,
+    metile/compile.py:168-178)."""
+
+    def __init__(self, model, verify, tolerance):
+        self.model = model
+        self.tolerance = tolerance
+        self.enabled = bool(verify)
+        self.failure = None
+        self.tokens = None
+        self.reference = None
+        self.magnitude = 1.0
+        if self.enabled:
+            try:
+                self.tokens = _probe_tokens(model)
+                self.reference = _decode_logits(model, self.tokens)
+                self.magnitude = max(float(self.reference.abs().max().item()), 1e-9)
+            except Exception as error:
+                self.failure = f"could not run the model unpatched ({type(error).__name__})"
+                self.enabled = False
+
+    def _distance(self):
+        return float((_decode_logits(self.model, self.tokens) - self.reference).abs().max().item())
+
+    def apply(self, selected):
+        """Patch the model with exactly `selected`; keep the patch only if the logits agree."""
+        from .integrations.torch_lm import apply_metile_to_torch_lm
+
+        selected = tuple(selected)
+        handle = apply_metile_to_torch_lm(model=self.model, **{name: name in selected for name in FEATURES})
+        handle.__enter__()
+        outcome = _Outcome(selected=selected, handle=handle)
+        if not self.enabled:
+            return outcome
+        try:
+            outcome.difference = self._distance()
+        except Exception:
+            outcome.ran = False
+            outcome.release()
+            return outcome
+        # `not (d <= bound)` rather than `d > bound`: a NaN distance must be rejected too.
+        if not outcome.difference <= self.tolerance * self.magnitude:
+            outcome.release()
+        return outcome
+
+    def explain(self, outcome):
+        """Why a single feature was declined, in the report's wording."""
+        if not outcome.ran or not outcome.difference:
+            return "could not run"
+        relative = outcome.difference / self.magnitude
+        if relative <= REORDERING_SCALE:
+            scale = "reduction-order scale, raise tolerance to keep it"
+        else:
+            scale = "far beyond rounding, so a different computation"
+        return f"changed the logits by {outcome.difference:g}, {relative:.1e} relative -- {scale}"
+
+
+def _largest_verified_set(verifier, requested, declined):
+    """The whole set if it verifies; otherwise every feature is judged alone and the survivors are
+    re-applied together (dropping the last one while the combination still disagrees)."""
+    outcome = verifier.apply(requested)
+    if outcome.accepted or not verifier.enabled:
+        return outcome
+    declined["combined"] = "the full feature set changed the logits; bisected"
+    survivors = []
+    for feature in requested:
+        alone = verifier.apply((feature,))
+        if alone.accepted:
+            alone.release()
+            survivors.append(feature)
+        else:
+            declined[feature] = verifier.explain(alone)
+    while survivors:
+        outcome = verifier.apply(survivors)
+        if outcome.accepted:
+            return outcome
+        survivors.pop()
+    return _Outcome(selected=())
+
+
 def compile(model, *, verify=True, features=FEATURES, tolerance=TOLERANCE):
     """Accelerate a torch model in place and report what changed.
 
@@ -135,94 +237,39 @@ def compile(model, *, verify=True, features=FEATURES, tolerance=TOLERANCE):
     implementations back.  `tolerance` is relative to the largest reference logit and defaults to
     exact; raising it to about 5e-3 admits differences at the scale of a summation reorder, and the
     report names every feature it declined and by how much."""
-    from .integrations.torch_lm import apply_metile_to_torch_lm
-
     if model is None or not callable(model):
         raise TypeError("compile expects a loaded model")
 
     name = type(getattr(model, "model", model)).__name__
     requested = tuple(feature for feature in FEATURES if feature in features)
     declined = {}
+    verifier = _Verifier(model, verify, tolerance)
+    if verifier.failure:
+        declined["verification"] = verifier.failure
 
-    reference = None
-    tokens = None
-    magnitude = 1.0
-    if verify:
-        try:
-            tokens = _probe_tokens(model)
-            reference = _decode_logits(model, tokens)
-            magnitude = max(float(reference.abs().max().item()), 1e-9)
-        except Exception as error:
-            declined["verification"] = f"could not run the model unpatched ({type(error).__name__})"
-            verify = False
-
-    def attempt(selected):
-        """Patch with `selected` enabled; return (handle, difference) or (None, difference)."""
-        flags = {feature: feature in selected for feature in FEATURES}
-        handle = apply_metile_to_torch_lm(model=model, **flags)
-        handle.__enter__()
-        if not verify:
-            return handle, None
-        try:
-            difference = float((_decode_logits(model, tokens) - reference).abs().max().item())
-        except Exception:
-            handle.__exit__(None, None, None)
-            return None, None
-        if not difference <= tolerance * magnitude:
-            handle.__exit__(None, None, None)
-            return None, difference
-        return handle, difference
-
-    handle, difference = attempt(requested)
-    kept = requested
-    if verify and handle is None:
-        declined["combined"] = "the full feature set changed the logits; bisected"
-        kept = []
-        for feature in requested:
-            trial, trial_difference = attempt([feature])
-            if trial is None:
-                if trial_difference:
-                    relative = trial_difference / magnitude
-                    scale = (
-                        "reduction-order scale, raise tolerance to keep it"
-                        if relative <= REORDERING_SCALE
-                        else "far beyond rounding, so a different computation"
-                    )
-                    declined[feature] = (
-                        f"changed the logits by {trial_difference:g}, {relative:.1e} relative -- {scale}"
-                    )
-                else:
-                    declined[feature] = "could not run"
-                continue
-            trial.__exit__(None, None, None)
-            kept.append(feature)
-        if kept:
-            handle, difference = attempt(kept)
-        if handle is None:
-            kept = []
-
-    if handle is None:
-        return CompileReport(model=name, verified=False if verify else None, declined=declined)
+    outcome = _largest_verified_set(verifier, requested, declined)
+    if not outcome.accepted:
+        return CompileReport(model=name, verified=False if verifier.enabled else None, declined=declined)
 
     surfaces = _surfaces(model)
     if not surfaces:
-        handle.__exit__(None, None, None)
+        outcome.release()
         declined["surfaces"] = "no layer in this model uses a class that can be replaced"
         return CompileReport(model=name, verified=None, declined=declined)
 
     # Per-call refusals recorded while the patched model ran: the original forward served those
     # calls; nothing was rerouted to another kernel.
-    for surface, reason in getattr(handle, "refusals", {}).items():
+    refusals = getattr(outcome.handle, "refusals", {})
+    for surface, reason in refusals.items():
         declined.setdefault(surface, f"refused at call time -- {reason}")
-    kept = tuple(feature for feature in kept if feature not in getattr(handle, "refusals", {}))
-
+    measured = verifier.enabled and outcome.difference is not None
     return CompileReport(
         model=name,
-        features=tuple(kept),
+        features=tuple(feature for feature in outcome.selected if feature not in refusals),
         surfaces=surfaces,
-        verified=None if not verify else True,
-        difference=difference,
-        relative=(difference / magnitude) if (verify and difference is not None) else None,
+        verified=True if verifier.enabled else None,
+        difference=outcome.difference,
+        relative=(outcome.difference / verifier.magnitude) if measured else None,
         declined=declined,
-        handle=handle,
+        handle=outcome.handle,
     )

@@ -24,6 +24,7 @@
 #define MT_FLAG_MLP_FUSED_MMA 0x80u  // mt_affine_mlp: insist on the warp-MMA single-launch kernel (M <= 8)
 #define MT_FLAG_HOST_PAIR 0x40u    // mt_affine_mlp_host: activations and residual share one host allocation
 #define MT_FLAG_MLP_FUSED 0x20u    // mt_affine_mlp: insist on the single-launch kernel (error if it does not apply)
+#define MT_FLAG_STREAM 0x100u     // half-SM tcgen05 kernel with exact weights (rows <= 32)
 #define MT_FLAG_GELU 0x10u        // dense activation: x/(1+exp(-1.702x)) instead of SiLU
 
 namespace mt {

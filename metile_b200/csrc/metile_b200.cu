@@ -7,6 +7,7 @@
 #include "affine_umma.cuh"
 #include "affine_mlp_fused.cuh"
 #include "affine_umma_scaled.cuh"
+#include "affine_stream.cuh"
 #include "common.cuh"
 #include "dense_rows.cuh"
 
@@ -52,7 +53,7 @@ static int check_affine_ptrs(const void* x, const uint32_t* w, const void* s, co
 // Llama-3.2-1B shape: 18.7 us vs 24.6 us) and loses from two rows on (26.1 us vs 24.7 us).
 static bool use_gemv(int M, unsigned int flags) {
     if (flags & MT_FLAG_FORCE_GEMV) return true;
-    if (flags & (MT_FLAG_FORCE_UMMA | MT_FLAG_UMMA_SMEM_A | MT_FLAG_UMMA_SCALED)) return false;
+    if (flags & (MT_FLAG_FORCE_UMMA | MT_FLAG_UMMA_SMEM_A | MT_FLAG_UMMA_SCALED | MT_FLAG_STREAM)) return false;
     return M <= 1;
 }
 
@@ -67,6 +68,10 @@ static int run_projection(const void* x, const AffineWeights& first, const Affin
         GemvWeights b = second ? GemvWeights{second->w, second->scales, second->biases} : a;
         return second ? launch_gemv<true>(x, a, b, residual, out, M, K, N, sms, stream)
                       : launch_gemv<false>(x, a, b, residual, out, M, K, N, sms, stream);
+    }
+    if (flags & MT_FLAG_STREAM) {
+        if (M > kStreamMaxRows) return MT_ERR_SHAPE;
+        return launch_stream(x, &first, second, residual, out, M, K, N, sms, stream);
     }
     if (flags & MT_FLAG_UMMA_SCALED) {
         if (M > 16) return MT_ERR_SHAPE;

@@ -56,9 +56,46 @@ def _model_layers(model):
     return list(layers) if layers is not None else []
 
 
+def _own_forward(cls):
+    """The `forward` a class (or one of its bases other than nn.Module) defines itself, else None.
+
+    nn.Module's own `forward` is a placeholder that raises; a class that inherits only that one has
+    nothing to replace (the reference makes the same point about `__call__`,
+    metile/integrations/mlx_lm.py:195-214)."""
+    for klass in cls.__mro__:
+        if klass is torch.nn.Module:
+            break
+        if "forward" in vars(klass):
+            return vars(klass)["forward"]
+    return None
+
+
+def _forward_source(cls):
+    import inspect
+
+    function = _own_forward(cls)
+    if function is None:
+        return None
+    try:
+        return inspect.getsource(function)
+    except (OSError, TypeError):
+        return None
+
+
 def _structurally_matches(cls, required):
-    """A class is a candidate when it defines its own forward and its instances carry the parts."""
-    return any("forward" in vars(klass) for klass in cls.__mro__ if klass is not torch.nn.Module)
+    """Whether `cls` is a candidate for the replacement that needs the attributes `required`.
+
+    The class must define its own forward, and every required name must be visible on the class: as a
+    class attribute or annotation, or -- torch modules bind their parts in __init__ -- in the source of
+    that forward.  So an attention class is not taken for a gated MLP, nor an MLP for a decoder block.
+    A structural match only admits a candidate; `compile` still verifies the logits."""
+    if _own_forward(cls) is None:
+        return False
+    annotations = getattr(cls, "__annotations__", {})
+    if all(hasattr(cls, name) or name in annotations for name in required):
+        return True
+    source = _forward_source(cls)
+    return source is not None and all(name in source for name in required)
 
 
 def _has_parts(module, required):
@@ -237,6 +274,12 @@ def apply_metile_to_torch_lm(model=None, *, attention=False, rms_norm=True, grap
     """
     if model is None:
         raise ValueError("apply_metile_to_torch_lm needs the model whose classes are to be patched")
+    # Every argument is checked before the first class is touched: an exception must not leave a
+    # half-applied patch behind with no handle to undo it.
+    if quantized_mlp_min_rows < 1:
+        raise ValueError("quantized MLP minimum rows must be positive")
+    if quantized_mlp_max_rows is not None and quantized_mlp_max_rows < quantized_mlp_min_rows:
+        raise ValueError("quantized MLP maximum rows must not be smaller than its minimum")
     patch = TorchPatch()
     if attention:
         patch.refuse("attention", "no decode-attention kernel in this package; the model's own attention runs")

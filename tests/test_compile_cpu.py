@@ -240,5 +240,78 @@ def test_row_gates_and_handle_context_manager(fake_kernels):
     assert not hasattr(FakeMLP.forward, "_metile_original")
     with pytest.raises(ValueError):
         torch_lm.apply_metile_to_torch_lm(model, quantized_mlp_min_rows=0)
+    # A refused call leaves nothing patched behind.
+    assert not hasattr(FakeBlock.forward, "_metile_original") and not hasattr(FakeMLP.forward, "_metile_original")
     with pytest.raises(ValueError):
         torch_lm.apply_metile_to_torch_lm(None)
+
+
+def test_structural_detection_excludes_as_well_as_admits():
+    """Structure has to exclude as well as admit (the reference's tests/test_compile.py:55-77): an
+    attention class is not a gated MLP, an MLP is not a decoder block, a norm is neither."""
+    from metile_b200.integrations import blocks
+
+    mlp_parts, block_parts = torch_lm._GATED_MLP_ATTRIBUTES, torch_lm._FUSED_BLOCK_ATTRIBUTES
+    for mlp_class in (FakeMLP, blocks.GatedMLP):
+        assert torch_lm._structurally_matches(mlp_class, mlp_parts)
+        assert not torch_lm._structurally_matches(mlp_class, block_parts)
+    for block_class in (FakeBlock, blocks.DecoderBlock):
+        assert torch_lm._structurally_matches(block_class, block_parts)
+        assert not torch_lm._structurally_matches(block_class, mlp_parts)
+    for other in (FakeAttention, blocks.Attention, FakeNorm, blocks.RMSNorm, FakeQuantizedLinear):
+        assert not torch_lm._structurally_matches(other, mlp_parts)
+        assert not torch_lm._structurally_matches(other, block_parts)
+    assert torch_lm._structurally_matches(FakeNorm, ("weight",))
+
+    class DeclaredParts(nn.Module):
+        """Parts declared on the class rather than bound in __init__ are seen as well."""
+
+        gate_proj: nn.Module
+        up_proj: nn.Module
+        down_proj: nn.Module
+
+        def forward(self, values):
+            return values
+
+    assert torch_lm._structurally_matches(DeclaredParts, mlp_parts)
+
+
+def test_structural_detection_needs_a_forward_to_replace():
+    """A class that defines no forward of its own has nothing to swap (tests/test_compile.py:80-94 of
+    the reference): nn.Module's inherited placeholder does not count."""
+
+    class HasThePartsButNoForward(nn.Module):
+        gate_proj = up_proj = down_proj = staticmethod(lambda x: x)
+
+    assert not torch_lm._structurally_matches(HasThePartsButNoForward, torch_lm._GATED_MLP_ATTRIBUTES)
+
+    class InheritsForward(FakeMLP):
+        pass
+
+    assert torch_lm._structurally_matches(InheritsForward, torch_lm._GATED_MLP_ATTRIBUTES)
+
+
+def test_an_attention_class_in_the_mlp_slot_is_not_patched(fake_kernels):
+    """A layer whose `mlp` is not a gated MLP keeps its own forward and `compile` says so."""
+    model = FakeLM()
+    for layer in model.layers:
+        layer.mlp = FakeAttention()
+    handle = torch_lm.apply_metile_to_torch_lm(model=model, rms_norm=False, graph_fusion=False, quantized_mlp=True)
+    try:
+        assert handle.replacements == []
+        assert getattr(FakeAttention.forward, "_metile_original", None) is None
+    finally:
+        handle.restore()
+
+
+def test_survivors_of_the_bisection_are_kept_together(fake_kernels):
+    """When the full set disagrees, the features that verify alone are applied together."""
+    fake_kernels["skew"] = 0.25  # the fused MLP is wrong; the norms are right
+    model = FakeLM()
+    report = metile_b200.compile(model, features=("rms_norm", "quantized_mlp"))
+    try:
+        assert report.features == ("rms_norm",)
+        assert "quantized_mlp" in report.declined and "combined" in report.declined
+        assert report.verified is True and report.difference == 0.0
+    finally:
+        report.restore()
