@@ -71,6 +71,14 @@ int mt_device_check(void);
  * device.  Returns 0, or -8 when words[0] != 0. */
 int mt_device_status(unsigned int words[4], int reset);
 
+/* Self-test of the bounded device-side waits: queues a tiny kernel whose wait can never be satisfied
+ * (which = 0: an mbarrier nobody arrives at; which = 1: the single-launch MLP's grid barrier with an
+ * unreachable target) and gives up after limit_us microseconds (1 ... 100000).  Nothing faults or
+ * hangs: the kernel records the wait code and returns, the next mt_device_status() reports -8 and,
+ * with reset != 0, clears the record and the grid-barrier counters.  Production kernels run the same
+ * wait code with a 2 s limit.  No counterpart in the reference project. */
+int mt_selftest_bounded_wait(int which, unsigned int limit_us, void* stream);
+
 /* y = x @ dequant(w)^T (+ residual, added to the un-rounded sum).
  * Replaces: metile/backends/mlx_quantized.py:691 (mlx_affine_qmv), :1538
  * (mlx_affine_residual_qmv), kernels/affine_qmv.py:57,94 and, for M > 1,

@@ -35,6 +35,7 @@ SIGNATURES = {
     "mt_status_string": (ctypes.c_char_p, [_i]),
     "mt_device_check": (_i, []),
     "mt_device_status": (_i, [ctypes.POINTER(ctypes.c_uint), _i]),
+    "mt_selftest_bounded_wait": (_i, [_i, _u, _p]),
     "mt_affine_qmv": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _u, _p]),
     "mt_affine_swiglu": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _u, _p]),
     "mt_affine_mlp_workspace_bytes": (_z, [_i, _i, _i]),

@@ -19,6 +19,34 @@ def stream_pointer(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def launch(function, device, *arguments):
+    """Call a C-ABI entry point with `device` current and that device's current stream as last argument.
+
+    The library takes its SM count, its per-device caches and its launches from the CURRENT device,
+    so the tensors' device is made current around the call; a model on cuda:1 works while cuda:0 is
+    current."""
+    with torch.cuda.device(device):
+        return function(*arguments, stream_pointer(device))
+
+
+def require_on_device(tensor, like, what, *, dtype=None, min_numel=None, contiguous=True):
+    """Check a tensor whose raw pointer is about to cross the C ABI: a CUDA tensor on the same
+    device as `like`, of the expected dtype, contiguous and at least `min_numel` elements long.
+    A CPU tensor or one on another GPU would otherwise reach the kernel as a foreign pointer."""
+    if tensor is None:
+        return
+    if not isinstance(tensor, torch.Tensor):
+        raise TypeError(f"{what} must be a torch tensor")
+    if not tensor.is_cuda or tensor.device != like.device:
+        raise ValueError(f"{what} must live on the activations' CUDA device ({like.device}), got {tensor.device}")
+    if dtype is not None and tensor.dtype != dtype:
+        raise ValueError(f"{what} must be {dtype}, got {tensor.dtype}")
+    if contiguous and not tensor.is_contiguous():
+        raise ValueError(f"{what} must be contiguous")
+    if min_numel is not None and tensor.numel() < min_numel:
+        raise ValueError(f"{what} holds {tensor.numel()} elements, needs at least {min_numel}")
+
+
 def require_cuda_bf16(values, what):
     if not isinstance(values, torch.Tensor):
         raise TypeError(f"{what} expects torch tensors")

@@ -12,7 +12,7 @@ import ctypes
 import torch
 
 from .. import _lib
-from ._common import library, pointer, require_cuda_bf16, rows_of, stream_pointer
+from ._common import launch, library, pointer, require_cuda_bf16, require_on_device, rows_of
 
 
 def mlx_rms_norm(values, weight, eps, *, autotune=True):
@@ -23,13 +23,14 @@ def mlx_rms_norm(values, weight, eps, *, autotune=True):
     if values.dtype != weight.dtype:
         raise TypeError("meTile RMSNorm requires matching input and weight dtypes")
     require_cuda_bf16(values, "meTile RMSNorm")
+    require_on_device(weight, values, "RMSNorm weight", contiguous=False)
     x = values.contiguous()
     w = weight.contiguous()
     out = torch.empty_like(x)
     if x.numel() == 0:
         return out
-    code = library().mt_rmsnorm(pointer(x), pointer(w), pointer(out), rows_of(x), x.shape[-1],
-                                ctypes.c_float(float(eps)), stream_pointer(x.device))
+    code = launch(library().mt_rmsnorm, x.device, pointer(x), pointer(w), pointer(out), rows_of(x), x.shape[-1],
+                  ctypes.c_float(float(eps)))
     _lib.check(code, "mlx_rms_norm")
     return out
 
@@ -44,6 +45,8 @@ def mlx_add_rms_norm(values, residual, weight, eps, *, autotune=True):
     if values.dtype != weight.dtype:
         raise TypeError("meTile fused add/RMSNorm requires matching input and weight dtypes")
     require_cuda_bf16(values, "meTile fused add/RMSNorm")
+    require_on_device(residual, values, "residual", contiguous=False)
+    require_on_device(weight, values, "RMSNorm weight", contiguous=False)
     x = values.contiguous()
     r = residual.contiguous()
     w = weight.contiguous()
@@ -51,8 +54,7 @@ def mlx_add_rms_norm(values, residual, weight, eps, *, autotune=True):
     normalized = torch.empty_like(x)
     if x.numel() == 0:
         return summed, normalized
-    code = library().mt_add_rmsnorm(pointer(x), pointer(r), pointer(w), pointer(summed),
-                                    pointer(normalized), rows_of(x), x.shape[-1],
-                                    ctypes.c_float(float(eps)), stream_pointer(x.device))
+    code = launch(library().mt_add_rmsnorm, x.device, pointer(x), pointer(r), pointer(w), pointer(summed),
+                  pointer(normalized), rows_of(x), x.shape[-1], ctypes.c_float(float(eps)))
     _lib.check(code, "mlx_add_rms_norm")
     return summed, normalized

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ._common import contiguous_2d, library, pointer, require_cuda_bf16, stream_pointer
+from ._common import contiguous_2d, launch, library, pointer, require_cuda_bf16, require_on_device
 
 
 def _check_dense(name, values, weight):
@@ -32,12 +32,12 @@ def mlx_dense_residual_qmv(values, weight, residual=None):
     expected = (*values.shape[:-1], weight.shape[0])
     if residual is not None and (tuple(residual.shape) != expected or residual.dtype != values.dtype):
         raise ValueError("residual must match the projection output shape and dtype")
+    require_on_device(residual, values, "residual", contiguous=False)
     x = contiguous_2d(values)
     res = None if residual is None else contiguous_2d(residual)
     out = torch.empty((x.shape[0], weight.shape[0]), dtype=values.dtype, device=values.device)
-    code = library().mt_dense_rows(pointer(x), pointer(weight), pointer(res), pointer(out),
-                                   x.shape[0], x.shape[1], weight.shape[0],
-                                   stream_pointer(values.device))
+    code = launch(library().mt_dense_rows, values.device, pointer(x), pointer(weight), pointer(res), pointer(out),
+                  x.shape[0], x.shape[1], weight.shape[0])
     _lib.check(code, name)
     return out.reshape(expected)
 
@@ -51,8 +51,7 @@ def mlx_dense_swiglu(values, gate_weight, up_weight):
         raise ValueError("dense SwiGLU requires matching gate/up weights")
     x = contiguous_2d(values)
     out = torch.empty((x.shape[0], gate_weight.shape[0]), dtype=values.dtype, device=values.device)
-    code = library().mt_dense_swiglu(pointer(x), pointer(gate_weight), pointer(up_weight),
-                                     pointer(out), x.shape[0], x.shape[1], gate_weight.shape[0],
-                                     stream_pointer(values.device))
+    code = launch(library().mt_dense_swiglu, values.device, pointer(x), pointer(gate_weight), pointer(up_weight),
+                  pointer(out), x.shape[0], x.shape[1], gate_weight.shape[0])
     _lib.check(code, name)
     return out.reshape(*values.shape[:-1], gate_weight.shape[0])

@@ -32,11 +32,12 @@ from .. import _lib
 from ._common import (
     check_affine_triple,
     contiguous_2d,
+    launch,
     library,
     pointer,
     require_cuda_bf16,
+    require_on_device,
     rows_of,
-    stream_pointer,
 )
 
 _state = threading.local()
@@ -105,14 +106,14 @@ def _project(name, values, weight, scales, biases, residual, group_size, bits):
     if residual is not None and (tuple(residual.shape) != expected_shape
                                  or residual.dtype != values.dtype):
         raise ValueError("residual must match the affine QMV output shape and dtype")
+    require_on_device(residual, values, "residual", contiguous=False)
     x = contiguous_2d(values)
     res = None if residual is None else contiguous_2d(residual)
     out = torch.empty((x.shape[0], output_features), dtype=values.dtype, device=values.device)
     flags = _flags()
-    code = library().mt_affine_qmv(pointer(x), pointer(weight), pointer(scales), pointer(biases),
-                                   pointer(res), pointer(out), x.shape[0], x.shape[1],
-                                   output_features, group_size, bits, flags,
-                                   stream_pointer(values.device))
+    code = launch(library().mt_affine_qmv, values.device, pointer(x), pointer(weight), pointer(scales),
+                  pointer(biases), pointer(res), pointer(out), x.shape[0], x.shape[1], output_features,
+                  group_size, bits, flags)
     _lib.check(code, name)
     return out.reshape(expected_shape), flags
 
@@ -159,11 +160,10 @@ def _swiglu(name, values, gate_weight, gate_scales, gate_biases, up_weight, up_s
     x = contiguous_2d(values)
     out = torch.empty((x.shape[0], output_features), dtype=values.dtype, device=values.device)
     flags = _flags()
-    code = library().mt_affine_swiglu(pointer(x), pointer(gate_weight), pointer(gate_scales),
-                                      pointer(gate_biases), pointer(up_weight), pointer(up_scales),
-                                      pointer(up_biases), pointer(out), x.shape[0], x.shape[1],
-                                      output_features, group_size, bits, flags,
-                                      stream_pointer(values.device))
+    code = launch(library().mt_affine_swiglu, values.device, pointer(x), pointer(gate_weight),
+                  pointer(gate_scales), pointer(gate_biases), pointer(up_weight), pointer(up_scales),
+                  pointer(up_biases), pointer(out), x.shape[0], x.shape[1], output_features, group_size,
+                  bits, flags)
     _lib.check(code, name)
     _record(_swiglu_dispatches, x.shape[0], x.shape[1], output_features, values.dtype, group_size,
             bits, flags)
@@ -206,7 +206,8 @@ def mlx_affine_mlp_executor(sample_values, gate_weight, gate_scales, gate_biases
     """Validate once and return `execute(values, residual)` = down(swiglu(values)) + residual.
 
     One C-ABI call (mt_affine_mlp) runs both kernels back to back on the current stream; the
-    bf16 hidden activations live in a workspace tensor allocated per call.  Unlike the
+    bf16 hidden activations live in a workspace the callable owns and grows on demand (calls of one
+    executor on different streams would share it: give each stream its own executor).  Unlike the
     reference (metile/backends/mlx_quantized.py:1806-1820) any row count is accepted and no
     1-row call is needed first.
     """
@@ -231,21 +232,29 @@ def mlx_affine_mlp_executor(sample_values, gate_weight, gate_scales, gate_biases
              down_scales, down_biases)
     pointers = [pointer(t) for t in bound]
 
+    workspace = {"hidden": None}  # grow-only scratch for the bf16 hidden activations, owned by the callable
+
     def execute(values, residual=None):
-        if values.dtype != torch.bfloat16 or values.shape[-1] != hidden_features:
+        if not isinstance(values, torch.Tensor) or values.dtype != torch.bfloat16 \
+                or values.shape[-1] != hidden_features:
             raise ValueError("affine MLP executor received activations of a different layout")
+        if not values.is_cuda or values.device != device:
+            raise ValueError(f"affine MLP executor is bound to {device}; activations are on {values.device}")
         x = contiguous_2d(values)
         res = None
         if residual is not None:
             if residual.shape != values.shape or residual.dtype != values.dtype:
                 raise ValueError("residual must match the MLP output shape and dtype")
+            require_on_device(residual, values, "residual", contiguous=False)
             res = contiguous_2d(residual)
         rows = x.shape[0]
-        hidden = torch.empty((rows, intermediate), dtype=torch.bfloat16, device=device)
+        hidden = workspace["hidden"]
+        if hidden is None or hidden.numel() < rows * intermediate:
+            hidden = workspace["hidden"] = torch.empty(rows * intermediate, dtype=torch.bfloat16, device=device)
         out = torch.empty((rows, hidden_features), dtype=torch.bfloat16, device=device)
-        code = lib.mt_affine_mlp(pointer(x), *pointers, pointer(res), pointer(hidden),
-                                 hidden.numel() * 2, pointer(out), rows, hidden_features,
-                                 intermediate, group_size, bits, _flags(), stream_pointer(device))
+        code = launch(lib.mt_affine_mlp, device, pointer(x), *pointers, pointer(res), pointer(hidden),
+                      hidden.numel() * 2, pointer(out), rows, hidden_features, intermediate, group_size, bits,
+                      _flags())
         _lib.check(code, name)
         return out.reshape(values.shape)
 
@@ -305,10 +314,9 @@ def mlx_affine_mlp_host_executor(max_rows, hidden_features, gate_weight, gate_sc
         if (residual is not None and residual.data_ptr() == values.data_ptr() + rows * row_bytes
                 and residual.untyped_storage().data_ptr() == values.untyped_storage().data_ptr()):
             flags |= _lib.FLAG_HOST_PAIR  # two views of one page-locked buffer: one copy moves both
-        code = lib.mt_affine_mlp_host(pointer(values), pointer(residual), pointer(out), stage_pointers[0],
-                                      residual_stage, stage_pointers[2], *pointers, pointer(workspace),
-                                      workspace.numel() * 2, rows, hidden_features, intermediate, group_size,
-                                      bits, flags, stream_pointer(device))
+        code = launch(lib.mt_affine_mlp_host, device, pointer(values), pointer(residual), pointer(out),
+                      stage_pointers[0], residual_stage, stage_pointers[2], *pointers, pointer(workspace),
+                      workspace.numel() * 2, rows, hidden_features, intermediate, group_size, bits, flags)
         _lib.check(code, name)
         return out
 

@@ -44,8 +44,6 @@
 
 #include <cuda.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -76,7 +74,8 @@ enum FusedWaitCode : unsigned int {
 };
 
 // Grid-barrier counters, one slot per launch in flight (launch n uses slot n % 64).  Every launch
-// adds exactly gridDim.x to its slot, so a slot is always a multiple of the grid size between uses.
+// adds exactly gridDim.x to its slot, so a slot is always a multiple of the grid size between uses --
+// unless a bounded wait gave up and left its slot short; mt_device_status(reset) zeroes the slots again.
 __device__ unsigned long long g_fused_barrier[kFusedBarrierSlots];
 
 struct FusedMlpParams {
@@ -96,18 +95,8 @@ struct FusedMlpParams {
     uint16_t* hidden;          // [1, I] bf16, written then read
     uint16_t* out;             // [1, H]
     unsigned long long* barrier;
-    long long* timeline;       // diagnostic phase stamps of CTA 0 (only in MT_TIMELINE builds), else null
     int M, H, I;
 };
-
-#ifdef MT_TIMELINE
-#define MT_FUSED_STAMP(slot)                                                                         \
-    do {                                                                                             \
-        if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.timeline[slot] = clock64(); \
-    } while (0)
-#else
-#define MT_FUSED_STAMP(slot) do { } while (0)
-#endif
 
 struct FusedMlpLayout {
     int rows1_max, rows2_max;  // most rows any CTA owns in each projection
@@ -248,7 +237,8 @@ __device__ __forceinline__ void fma_shares(const uint4 (&pk)[kN], const uint32_t
 
 // The grid-wide barrier, called by the compute warps: every CTA arrives once; the slot grows by
 // gridDim.x per launch.
-__device__ __forceinline__ void fused_grid_barrier(unsigned long long* slot, int grid, volatile int* abort_flag) {
+__device__ __forceinline__ void fused_grid_barrier(unsigned long long* slot, int grid, volatile int* abort_flag,
+                                                   unsigned long long limit_ns = ptx::kWaitLimitNs) {
     fused_compute_sync();  // orders this CTA's stores before thread 0's release
     if (threadIdx.x == 0) {
         // Release: this CTA's stores are visible to whoever acquires the counter afterwards; the
@@ -257,7 +247,7 @@ __device__ __forceinline__ void fused_grid_barrier(unsigned long long* slot, int
         const unsigned long long target = (arrived / (unsigned long long)grid + 1ull) * (unsigned long long)grid;
         const unsigned long long start = ptx::global_timer_ns();
         while (ptx::ld_acquire_gpu_u64(slot) < target) {
-            if (ptx::global_timer_ns() - start > ptx::kWaitLimitNs) {
+            if (ptx::global_timer_ns() - start > limit_ns) {
                 if (atomicCAS(&g_device_status[0], 0u, (unsigned int)kWaitFusedGrid) == 0u) {
                     g_device_status[1] = blockIdx.x;
                     g_device_status[2] = threadIdx.x;
@@ -354,7 +344,6 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     uint64_t* empty_bar = full_bar + kFusedMaxSlots;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kFusedMaxSlots);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    MT_FUSED_STAMP(0);
 
     const int row1 = (int)((unsigned)I * (unsigned)cta / (unsigned)grid);
     const int n1 = (int)((unsigned)I * (unsigned)(cta + 1) / (unsigned)grid) - row1;
@@ -375,7 +364,6 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
         ptx::mbar_fence_init();
     }
     __syncthreads();
-    MT_FUSED_STAMP(1);
     ptx::griddep_launch_dependents();
 
     if (warp == kFusedComputeWarps) {
@@ -385,7 +373,6 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
 
     // ---------------------------------------------------------------------- compute warps
     ptx::griddep_wait();  // the activations and the residual are the preceding kernel's output
-    MT_FUSED_STAMP(3);
     float residual_value = 0.0f;  // fetched now, used at the very end
     if ((int)threadIdx.x < n2 * kM && p.residual) {
         const int row = threadIdx.x / kM, m = threadIdx.x - row * kM;
@@ -401,12 +388,10 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
         const int group = (set * 16 + (lane >> 1)) * 2;  // byte offset of their scale in a row of scales
         LaneActivations<kM> x;
         load_lane_activations<kM, false>(p.x, H, set * 1024 + lane * 32, x);
-        MT_FUSED_STAMP(4);
         for (int it = 0; it < items1 && alive; ++it) {
             const int slot = it % slots, use = it / slots;
             if (!ptx::mbar_wait(&full_bar[slot], (uint32_t)use & 1u, abort_flag, kWaitFusedFull)) { alive = false; break; }
             __syncwarp();
-            if (it < 4) MT_FUSED_STAMP(5 + it);
             const uint8_t* item = ring + (size_t)slot * lay.item_bytes;
             const uint8_t* tables = item + 2 * kFusedItemRows * rb1;
             const int share_rows = 2 * min(kFusedItemRows, n1 - kFusedItemRows * it);
@@ -434,7 +419,6 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
                         }
                 }
             }
-            if (it < 8) MT_FUSED_STAMP(20 + it);
             // The slot was read with ordinary loads; if the copy engine will overwrite it, order the two.
             if (it + slots < items1 + items2) {
                 ptx::fence_proxy_async_smem();
@@ -442,9 +426,7 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
                 if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
             }
         }
-        MT_FUSED_STAMP(9);
         fused_compute_sync();
-        MT_FUSED_STAMP(10);
         for (int idx = threadIdx.x; idx < n1 * kM; idx += kFusedComputeThreads) {
             const int row = idx / kM, m = idx - row * kM;
             float gate = 0.0f, up = 0.0f;
@@ -455,9 +437,7 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
             p.hidden[(size_t)m * I + row1 + row] = f32_to_bf16_bits(swiglu_f32(gate, up));
         }
     }
-    MT_FUSED_STAMP(11);
     fused_grid_barrier(p.barrier, grid, abort_flag);
-    MT_FUSED_STAMP(12);
     {
         // ------------------------------------------------------------------ down
         const int sets = lay.sets2, step = kFusedComputeWarps / sets;
@@ -466,13 +446,11 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
         const int group = (set * 16 + (lane >> 1)) * 2;
         LaneActivations<kM> x;
         load_lane_activations<kM, true>(p.hidden, I, set * 1024 + lane * 32, x);
-        MT_FUSED_STAMP(13);
         for (int j = 0; j < items2 && alive; ++j) {
             const int it = items1 + j;
             const int slot = it % slots, use = it / slots;
             if (!ptx::mbar_wait(&full_bar[slot], (uint32_t)use & 1u, abort_flag, kWaitFusedFull)) { alive = false; break; }
             __syncwarp();
-            if (j == 0) MT_FUSED_STAMP(14);
             const uint8_t* item = ring + (size_t)slot * lay.item_bytes;
             const uint8_t* tables = item + lay.down_rows * rb2;
             const int rows_here = min(lay.down_rows, n2 - lay.down_rows * j);
@@ -505,7 +483,6 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
                 if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
             }
         }
-        MT_FUSED_STAMP(15);
         fused_compute_sync();
         if ((int)threadIdx.x < n2 * kM) {
             const int row = threadIdx.x / kM, m = threadIdx.x - row * kM;
@@ -514,7 +491,6 @@ affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
             p.out[(size_t)m * H + row2 + row] = f32_to_bf16_bits(v + residual_value);
         }
     }
-    MT_FUSED_STAMP(16);
 }
 
 // ===================================================================================================
@@ -1005,20 +981,27 @@ inline int launch_mlp_fused_rows(const FusedMlpParams& params, int sm_count, int
     return launch_mlp_fused_kernel<kM>(affine_mlp_fused_kernel<kM>, smem, params, sm_count, device, stream);
 }
 
-// Caller has checked fused_mlp_applicable(), or fused_mlp_mma_applicable() when `mma` is set.
-inline int launch_mlp_fused(FusedMlpParams params, int sm_count, bool mma, cudaStream_t stream) {
+// The barrier slot of the next launch on the current device (slots rotate, one per launch in flight).
+inline unsigned long long* next_fused_barrier_slot() {
     static unsigned long long* slots[64] = {};
     static unsigned int launches = 0;
     int device = 0;
-    cudaGetDevice(&device);
-    if (device >= 64) return MT_ERR_DEVICE;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
     if (!slots[device]) {
-        if (getenv("MT_FUSED_NO_PDL")) g_fused_pdl_state[device] = -1;  // diagnostic switch
         void* address = nullptr;
-        if (cudaGetSymbolAddress(&address, g_fused_barrier) != cudaSuccess) return MT_ERR_LAUNCH;
+        if (cudaGetSymbolAddress(&address, g_fused_barrier) != cudaSuccess) return nullptr;
         slots[device] = static_cast<unsigned long long*>(address);
     }
-    params.barrier = slots[device] + (__atomic_fetch_add(&launches, 1u, __ATOMIC_RELAXED) % kFusedBarrierSlots);
+    return slots[device] + (__atomic_fetch_add(&launches, 1u, __ATOMIC_RELAXED) % kFusedBarrierSlots);
+}
+
+// Caller has checked fused_mlp_applicable(), or fused_mlp_mma_applicable() when `mma` is set.
+inline int launch_mlp_fused(FusedMlpParams params, int sm_count, bool mma, cudaStream_t stream) {
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 64) return MT_ERR_DEVICE;
+    params.barrier = next_fused_barrier_slot();
+    if (!params.barrier) return MT_ERR_LAUNCH;
     if (mma) {
         if (!encode_weight_map(&params.gate_map, params.gate_w, params.H, params.I, kFusedItemRows) ||
             !encode_weight_map(&params.up_map, params.up_w, params.H, params.I, kFusedItemRows))

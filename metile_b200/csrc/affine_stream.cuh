@@ -28,11 +28,12 @@
 // predecessor's results arrive: the weight stream from HBM does not stop between kernels.
 //
 //   producer lane : TMA boxes of 128 rows x 128 B (four k-blocks of one tile), 128B swizzle, ring
-//                   of six boxes
+//                   of five boxes
 //   dequant warps : 8 = two groups of four warps (128 rows).  gate|up: group t feeds tile t.
 //                   Single projection: group d takes the k-blocks i = d (mod 2).
-//   x warp        : activation chunks (L2-resident) -> swizzled B tile in the element order the
-//                   unpack produces (e0,e4,e1,e5,e2,e6,e3,e7); group sums X -> shared table
+//   x warp        : activation chunks (L2-resident, cp.async) -> ring of swizzled B tiles in the
+//                   element order the unpack produces (e0,e4,e1,e5,e2,e6,e3,e7); group sums X -> shared
+//                   table; runs ahead of the weight pipeline, two k-blocks per hand-over
 //   MMA lane      : four tcgen05.mma (M=128, K=16) per k-block and tile into that stage's OWN
 //                   partial accumulator, tcgen05.commit
 //   fold          : the dequant thread that refills a stage first reads the stage's finished
@@ -61,27 +62,31 @@ struct StreamConfig {
     static constexpr int kXWarp = kDequantWarps + 2;
     static constexpr int kThreads = (kDequantWarps + 3) * 32;
     static constexpr int kBoxBytes = kUmmaTileRows * 128;      // one tile, four k-blocks
-    static constexpr int kRingBoxes = 6;
+    static constexpr int kRingBoxes = 5;
     static constexpr int kRingBytes = kRingBoxes * kBoxBytes;
     static constexpr int kBBytes = kNPad * 128;
-    static constexpr int kXTasks = kNPad * 8 / 32;             // 16-byte activation chunks per lane and k-block
-    static constexpr int kXsumEntries = 4 * kStages;           // ring of group-sum rows, indexed by k-block
+    static constexpr int kBSlots = 4;                          // ring of activation (B) tiles, indexed by k-block
+    static constexpr int kXBatch = 2;                          // k-blocks the x warp prepares per iteration
+    static constexpr int kXDepth = 2;                          // batches of raw activation chunks in flight (cp.async)
+    static constexpr int kXsumEntries = 16;                    // ring of group-sum rows, indexed by k-block
+    static constexpr int kXStageBytes = kXDepth * kXBatch * kNPad * 128;
     static constexpr int kXsumBytes = kXsumEntries * kNPad * 4;
     static constexpr int kACols = kStages * kT * 32;
     static constexpr int kPCols = kStages * kT * kNPad;
     static constexpr int kTmemCols = pow2_at_least(kACols + kPCols);
     static constexpr int kStagingBytes = kDepth * kT * kNPad * kUmmaTileRows * 4;
-    static constexpr int kDataBytes = kRingBytes + kStages * kBBytes + kXsumBytes;
-    static constexpr int kBarrierBytes = 8 * (2 * kRingBoxes + 2 * kStages) + 16;
+    static constexpr int kDataBytes = kRingBytes + kBSlots * kBBytes + kXStageBytes + kXsumBytes;
+    static constexpr int kBarrierBytes = 8 * (2 * kRingBoxes + 2 * kStages + 2 * kBSlots) + 16;
     static constexpr int kSmemBytes = 1024 + kDataBytes + kBarrierBytes;
     static constexpr int kPerSm = kNPad <= 16 ? 2 : 1;         // CTAs (of consecutive launches) per SM
-    static constexpr int kFullArrivals = kDequantWarps / kDepth + 1;  // warps that fill one stage + the x warp
+    static constexpr int kFullArrivals = kDequantWarps / kDepth;      // warps that fill one A stage
     static_assert(kT == 1 || kT == 2, "one tile, or a gate tile and an up tile");
     static_assert(kNPad == 16 || kNPad == 32, "activation rows are padded to 16 or 32");
     static_assert(kPerSm * kTmemCols <= 512, "tensor memory budget");
     static_assert(kPerSm * (kSmemBytes + 1024) <= 227 * 1024, "shared memory budget");
     static_assert(kStagingBytes <= kRingBytes, "the epilogue reuses the ring");
-    static_assert(kUmmaKBlocksPerSlot % kStages == 0 || kStages % kUmmaKBlocksPerSlot == 0, "static stage indices");
+    static_assert(kBSlots % kStages == 0 && kBSlots % kXBatch == 0, "static stage and slot indices in the MMA loop");
+    static_assert(kXsumEntries > kBSlots + kStages && (kXsumEntries & (kXsumEntries - 1)) == 0, "group sums outlive their fold");
 };
 
 enum : unsigned int {
@@ -124,13 +129,16 @@ affine_stream_kernel(const __grid_constant__ UmmaParams p) {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* ring = smem;
     uint8_t* b_tiles = smem + Cfg::kRingBytes;
-    float* xsum = reinterpret_cast<float*>(b_tiles + Cfg::kStages * Cfg::kBBytes);  // [k-block % entries][kNPad]
+    uint8_t* x_stage = b_tiles + Cfg::kBSlots * Cfg::kBBytes;                       // [batch % depth][task] x 16 B
+    float* xsum = reinterpret_cast<float*>(x_stage + Cfg::kXStageBytes);            // [k-block % entries][kNPad]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kDataBytes);
     uint64_t* ring_full = bars;
     uint64_t* ring_empty = ring_full + Cfg::kRingBoxes;
-    uint64_t* st_full = ring_empty + Cfg::kRingBoxes;   // stage filled: dequant warps + x warp -> MMA lane
-    uint64_t* st_done = st_full + Cfg::kStages;         // stage consumed: MMA commit + x warp -> everybody
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(st_done + Cfg::kStages);
+    uint64_t* st_full = ring_empty + Cfg::kRingBoxes;   // A stage filled: dequant warps -> MMA lane
+    uint64_t* st_done = st_full + Cfg::kStages;         // A stage and its partial tile consumed: MMA commit -> dequant warps
+    uint64_t* b_full = st_done + Cfg::kStages;          // B tile and group sums written: x warp -> MMA lane, dequant warps
+    uint64_t* b_free = b_full + Cfg::kBSlots;           // B tile consumed: MMA commit -> x warp
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_free + Cfg::kBSlots);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -156,7 +164,11 @@ affine_stream_kernel(const __grid_constant__ UmmaParams p) {
         }
         for (int i = 0; i < Cfg::kStages; ++i) {
             ptx::mbar_init(&st_full[i], Cfg::kFullArrivals);
-            ptx::mbar_init(&st_done[i], 2);
+            ptx::mbar_init(&st_done[i], 1);
+        }
+        for (int i = 0; i < Cfg::kBSlots; ++i) {
+            ptx::mbar_init(&b_full[i], 1);
+            ptx::mbar_init(&b_free[i], 1);
         }
         *abort_flag = 0;
         ptx::mbar_fence_init();
@@ -208,12 +220,17 @@ affine_stream_kernel(const __grid_constant__ UmmaParams p) {
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::umma_idesc_bf16(kUmmaTileRows, kNPad);
             const uint64_t desc0 = ptx::smem_desc_k_major_sw128(ptx::smem_u32(b_tiles));
-            for (int i0 = 0; i0 < nkb; i0 += Cfg::kStages) {
-                const uint32_t phase = (uint32_t)(i0 / Cfg::kStages) & 1u;
+            for (int i0 = 0; i0 < nkb; i0 += Cfg::kBSlots) {
+                const uint32_t b_phase = (uint32_t)(i0 / Cfg::kBSlots) & 1u;
 #pragma unroll
-                for (int a = 0; a < Cfg::kStages; ++a) {
-                    if (i0 + a >= nkb) break;
-                    if (!ptx::mbar_wait(&st_full[a], phase, abort_flag, kWaitStreamStageFull)) { i0 = nkb; break; }
+                for (int u = 0; u < Cfg::kBSlots; ++u) {
+                    const int i = i0 + u;
+                    if (i >= nkb) break;
+                    constexpr int kUsesPerRound = Cfg::kBSlots / Cfg::kStages;  // uses of an A stage per round of B slots
+                    const int a = u % Cfg::kStages;
+                    const uint32_t a_phase = (uint32_t)((i0 / Cfg::kBSlots) * kUsesPerRound + u / Cfg::kStages) & 1u;
+                    if (!ptx::mbar_wait(&b_full[u], b_phase, abort_flag, kWaitStreamStageFull) ||
+                        !ptx::mbar_wait(&st_full[a], a_phase, abort_flag, kWaitStreamStageFull)) { i0 = nkb; break; }
                     ptx::tc_fence_after_sync();
 #pragma unroll
                     for (int ks = 0; ks < kUmmaBlockK / 16; ++ks) {
@@ -221,70 +238,95 @@ affine_stream_kernel(const __grid_constant__ UmmaParams p) {
                         for (int tt = 0; tt < kT; ++tt) {
                             const uint32_t d_tmem = tmem_base + Cfg::kACols + (a * kT + tt) * kNPad;
                             const uint32_t a_tmem = tmem_base + (a * kT + tt) * 32 + ks * 8;
-                            const uint64_t b_desc = desc0 + (uint64_t)((a * Cfg::kBBytes + ks * 32) >> 4);
+                            const uint64_t b_desc = desc0 + (uint64_t)((u * Cfg::kBBytes + ks * 32) >> 4);
                             ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, ks > 0 ? 1u : 0u);
                         }
                     }
                     ptx::umma_commit(&st_done[a]);
+                    ptx::umma_commit(&b_free[u]);
                 }
             }
         }
     } else if (warp == Cfg::kXWarp) {
-        // ------------------------------------------------------------------ activation tile + group sums
-        // Lane l, task q: activation row 4 q + l / 8, 16-byte chunk l % 8 of the k-block.  A row's eight
-        // chunks sit in eight neighbouring lanes, whose sums meet in a fixed butterfly: X does not
-        // depend on how many rows there are.
+        // ------------------------------------------------------------------ activation tiles + group sums
+        // Task = (k-block of the batch, activation row, 16-byte chunk of the k-block's 64 columns); lane l
+        // takes the tasks l, l + 32, ...  The eight chunks of one (k-block, row) are eight neighbouring
+        // tasks, hence eight neighbouring lanes, whose sums meet in a fixed butterfly: a group sum does
+        // not depend on how many rows there are.  kXBatch k-blocks are prepared per iteration so that the
+        // cross-proxy fence and the hand-over are paid once per batch.
         ptx::griddep_wait();  // the activations are the preceding kernel's output
-        const int row0 = lane >> 3, c = lane & 7;
-        const uint16_t* x_base = p.x + (size_t)kb_begin * kUmmaBlockK + c * 8;
-        uint4 xv_next[Cfg::kXTasks];
-        auto load_x = [&](int kblock) {
-#pragma unroll
-            for (int q = 0; q < Cfg::kXTasks; ++q) {
-                const int row = 4 * q + row0;
-                xv_next[q] = make_uint4(0u, 0u, 0u, 0u);
-                if (row < p.M)
-                    xv_next[q] = ptx::ld_global_dependent_u4(x_base + (size_t)row * p.K + (size_t)kblock * kUmmaBlockK);
-            }
-        };
-        if (nkb > 0) load_x(0);
-        for (int i = 0; i < nkb; ++i) {
-            const int a = i % Cfg::kStages;
-            const uint32_t use = (uint32_t)(i / Cfg::kStages);
-            uint4 xv[Cfg::kXTasks];
-#pragma unroll
-            for (int q = 0; q < Cfg::kXTasks; ++q) xv[q] = xv_next[q];
-            if (i + 1 < nkb) load_x(i + 1);
-            const bool ok = ptx::mbar_wait(&st_done[a], (use & 1u) ^ 1u, abort_flag, kWaitStreamStageFree);
-            if (!__all_sync(0xFFFFFFFFu, ok)) break;
-            uint8_t* b_tile = b_tiles + a * Cfg::kBBytes;
-            float* sums = xsum + (i % Cfg::kXsumEntries) * kNPad;
-#pragma unroll
-            for (int q = 0; q < Cfg::kXTasks; ++q) {
-                const int row = 4 * q + row0;
-                if (4 * q < p.M) {  // warp-uniform: the shuffles below need all lanes of the row groups in use
-                    uint4 o;
-                    o.x = __byte_perm(xv[q].x, xv[q].z, 0x5410);  // (x0, x4)
-                    o.y = __byte_perm(xv[q].x, xv[q].z, 0x7632);  // (x1, x5)
-                    o.z = __byte_perm(xv[q].y, xv[q].w, 0x5410);  // (x2, x6)
-                    o.w = __byte_perm(xv[q].y, xv[q].w, 0x7632);  // (x3, x7)
-                    *reinterpret_cast<uint4*>(b_tile + row * 128 + ((c ^ (row & 7)) << 4)) = o;
-                    float part = ((bf16_lo(xv[q].x) + bf16_hi(xv[q].x)) + (bf16_lo(xv[q].y) + bf16_hi(xv[q].y))) +
-                                 ((bf16_lo(xv[q].z) + bf16_hi(xv[q].z)) + (bf16_lo(xv[q].w) + bf16_hi(xv[q].w)));
-                    part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
-                    part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
-                    part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
-                    if (c == 0) sums[row] = part;
+        const int tasks_per_kb = p.M * 8;
+        const int tasks = Cfg::kXBatch * tasks_per_kb;
+        const int trips = (tasks + 31) >> 5;
+        const uint16_t* x_base = p.x + (size_t)kb_begin * kUmmaBlockK;
+        constexpr int kBatchChunks = Cfg::kXBatch * kNPad * 8;  // 16-byte chunks of one staging slot
+        // The chunks come from L2 (several hundred cycles away), so kXDepth batches are kept in flight
+        // with cp.async into a small ring; a lane reads back only the chunks it copied itself.  One
+        // group is committed per batch, empty or not, so that the group count stays uniform.
+        auto issue_x = [&](int batch) {
+            const int kb0 = batch * Cfg::kXBatch;
+            if (kb0 < nkb) {
+                for (int trip = 0; trip < trips; ++trip) {
+                    const int task = trip * 32 + lane;
+                    const int kbl = task >= tasks_per_kb ? 1 : 0;
+                    const int rem = task - kbl * tasks_per_kb;
+                    if (task < tasks && kb0 + kbl < nkb)
+                        ptx::cp_async_16(ptx::smem_u32(x_stage) + (uint32_t)(((batch % Cfg::kXDepth) * kBatchChunks + task) * 16),
+                                         x_base + (size_t)(rem >> 3) * p.K + (size_t)(kb0 + kbl) * kUmmaBlockK + (rem & 7) * 8);
                 }
             }
-            // The B tile is read by the tensor core (async proxy).
+            ptx::cp_async_commit();
+        };
+        static_assert(Cfg::kXBatch == 2, "the task decoding above assumes two k-blocks per batch");
+        const int batches = (nkb + Cfg::kXBatch - 1) / Cfg::kXBatch;
+#pragma unroll
+        for (int d = 0; d < Cfg::kXDepth; ++d) issue_x(d);
+        for (int batch = 0; batch < batches; ++batch) {
+            const int kb0 = batch * Cfg::kXBatch;
+            ptx::cp_async_wait_group<Cfg::kXDepth - 1>();
+            bool ok = true;
+#pragma unroll
+            for (int kbl = 0; kbl < Cfg::kXBatch; ++kbl) {
+                const int kb = kb0 + kbl;
+                if (kb < nkb)
+                    ok = ok && ptx::mbar_wait(&b_free[kb % Cfg::kBSlots], ((uint32_t)(kb / Cfg::kBSlots) & 1u) ^ 1u, abort_flag,
+                                              kWaitStreamStageFree);
+            }
+            if (!__all_sync(0xFFFFFFFFu, ok)) break;
+            for (int trip = 0; trip < trips; ++trip) {
+                const int task = trip * 32 + lane;
+                const int kbl = task >= tasks_per_kb ? 1 : 0;
+                const int rem = task - kbl * tasks_per_kb;
+                const int row = rem >> 3, c = rem & 7, kb = kb0 + kbl;
+                const bool active = task < tasks && kb < nkb;
+                float part = 0.0f;
+                if (active) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(x_stage + ((batch % Cfg::kXDepth) * kBatchChunks + task) * 16);
+                    uint4 o;
+                    o.x = __byte_perm(v.x, v.z, 0x5410);  // (x0, x4)
+                    o.y = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
+                    o.z = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
+                    o.w = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
+                    *reinterpret_cast<uint4*>(b_tiles + (kb % Cfg::kBSlots) * Cfg::kBBytes + row * 128 + ((c ^ (row & 7)) << 4)) = o;
+                    part = ((bf16_lo(v.x) + bf16_hi(v.x)) + (bf16_lo(v.y) + bf16_hi(v.y))) +
+                           ((bf16_lo(v.z) + bf16_hi(v.z)) + (bf16_lo(v.w) + bf16_hi(v.w)));
+                }
+                part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
+                part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
+                part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
+                if (active && c == 0) xsum[(kb & (Cfg::kXsumEntries - 1)) * kNPad + row] = part;
+            }
+            issue_x(batch + Cfg::kXDepth);  // reuses the staging slot that was just read
+            // The B tiles are read by the tensor core (async proxy).
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                ptx::mbar_arrive(&st_full[a]);
-                ptx::mbar_arrive(&st_done[a]);  // publishes `sums` to whoever waits for the stage's MMAs
+#pragma unroll
+                for (int kbl = 0; kbl < Cfg::kXBatch; ++kbl)
+                    if (kb0 + kbl < nkb) ptx::mbar_arrive(&b_full[(kb0 + kbl) % Cfg::kBSlots]);
             }
         }
+        ptx::cp_async_wait_group<0>();  // nothing of this thread's is in flight when the CTA ends
     } else {
         // ------------------------------------------------------------------ dequant + fold warps
         const int group = warp >> 2;                       // four warps = 128 rows
@@ -386,11 +428,17 @@ affine_stream_kernel(const __grid_constant__ UmmaParams p) {
                 }
                 ptx::tc_wait_st();
                 ptx::tc_fence_before_sync();
-                __syncwarp();
+                // The group sums of k-block i are read when its partial tile is folded, kQueue iterations
+                // from now.  Observing the x warp's hand-over of that k-block here -- before this warp's own
+                // hand-over, without which the k-block's MMAs cannot run and its B slot cannot be reused --
+                // is what orders those reads after the x warp's writes.
+                const bool sums_ready = ptx::mbar_wait(&b_full[i % Cfg::kBSlots], (uint32_t)(i / Cfg::kBSlots) & 1u, abort_flag,
+                                                       kWaitStreamStageFull);
+                if (!__all_sync(0xFFFFFFFFu, sums_ready)) { alive = false; break; }
                 if (lane == 0) ptx::mbar_arrive(&st_full[a]);
 
-                // The group sums of the folded k-block stay valid: the x warp reuses a table row only
-                // 4 * kStages k-blocks later, which needs this thread's NEXT hand-over of the stage.
+                // The group sums of the folded k-block are still there: the x warp reuses a table row
+                // kXsumEntries k-blocks later, which needs hand-overs this thread has not made yet.
                 if (folding) {
                     const float* sums = xsum + ((i - Cfg::kStages) & (Cfg::kXsumEntries - 1)) * kNPad;
                     fold16(part, 0, pend_scale[q_slot], pend_offset[q_slot], sums);

@@ -475,7 +475,6 @@ inline int launch_umma_scaled_any(const void* x, const AffineWeights* first, con
     params.M = M;
     params.K = K;
     params.N = N;
-    params.timeline = nullptr;
     params.ksplit = swiglu ? umma_ksplit<2, true, true>(tiles, slots_total) : umma_ksplit<1, true, false>(tiles, slots_total);
     const int per_cta = ((slots_total + params.ksplit - 1) / params.ksplit) * kUmmaKBlocksPerSlot;
     if (per_cta > UmmaScaledConfig<1>::kMaxKBlocks) return MT_ERR_SHAPE;

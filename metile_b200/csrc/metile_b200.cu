@@ -156,6 +156,31 @@ static int static_hidden_address(void** out) {
     return MT_OK;
 }
 
+// ---- self-test kernels: make a bounded device-side wait run out, on purpose and harmlessly ----------
+constexpr unsigned int kWaitSelfTest = 0x7E1;
+
+// One CTA waits on an mbarrier nobody arrives at; the wait gives up after `limit_ns` and returns.
+__global__ void selftest_mbarrier_wait_kernel(unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        abort_flag = 0;
+        ptx::mbar_fence_init();
+    }
+    __syncthreads();
+    ptx::mbar_wait(&bar, 0, &abort_flag, kWaitSelfTest, limit_ns);
+}
+
+// Two CTAs meet at the single-launch MLP's grid barrier with a target no arrival count can reach.
+__global__ void __launch_bounds__(kFusedComputeThreads)
+selftest_grid_barrier_kernel(unsigned long long* slot, unsigned long long limit_ns) {
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) abort_flag = 0;
+    __syncthreads();
+    fused_grid_barrier(slot, (int)gridDim.x + 1, &abort_flag, limit_ns);
+}
+
 }  // namespace mt
 
 using namespace mt;
@@ -179,14 +204,6 @@ const char* mt_status_string(int status) {
     }
 }
 
-// Diagnostic hook (not part of the public header): phase stamps of the tcgen05 kernel.
-int mt_debug_fused_pdl_state(void) {
-    int device = 0;
-    cudaGetDevice(&device);
-    return device < 64 ? g_fused_pdl_state[device] : 0;
-}
-void mt_debug_set_timeline(void* device_buffer) { g_timeline_buffer = static_cast<long long*>(device_buffer); }
-
 int mt_device_check(void) { return device_is_sm100() ? MT_OK : MT_ERR_DEVICE; }
 
 int mt_device_status(unsigned int words[4], int reset) {
@@ -196,8 +213,30 @@ int mt_device_status(unsigned int words[4], int reset) {
     if (reset) {
         const unsigned int zeros[4] = {0, 0, 0, 0};
         if (cudaMemcpyToSymbol(g_device_status, zeros, sizeof(zeros)) != cudaSuccess) return MT_ERR_LAUNCH;
+        // A wait that gave up at the single-launch MLP's grid barrier leaves its counter short of a
+        // multiple of the grid size; the device is idle here, so every counter can start over.
+        static const unsigned long long no_arrivals[kFusedBarrierSlots] = {};
+        if (words[0] && cudaMemcpyToSymbol(g_fused_barrier, no_arrivals, sizeof(no_arrivals)) != cudaSuccess)
+            return MT_ERR_LAUNCH;
     }
     return words[0] ? MT_ERR_DEVICE_WAIT : MT_OK;
+}
+
+int mt_selftest_bounded_wait(int which, unsigned int limit_us, void* stream) {
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    if (limit_us < 1 || limit_us > 100000) return MT_ERR_SHAPE;  // 1 us ... 100 ms
+    const unsigned long long limit_ns = 1000ull * limit_us;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (which == 0) {
+        selftest_mbarrier_wait_kernel<<<1, 64, 0, s>>>(limit_ns);
+    } else if (which == 1) {
+        unsigned long long* slot = next_fused_barrier_slot();
+        if (!slot) return MT_ERR_LAUNCH;
+        selftest_grid_barrier_kernel<<<2, kFusedComputeThreads, 0, s>>>(slot, limit_ns);
+    } else {
+        return MT_ERR_SHAPE;
+    }
+    return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
 }
 
 int mt_affine_qmv(const void* x, const uint32_t* w, const void* scales, const void* biases, const void* residual,
@@ -249,6 +288,16 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
     if (M == 0) return MT_OK;
     if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < mt_affine_mlp_workspace_bytes(M, H, I))
         return MT_ERR_WORKSPACE;
+    // Every operand of all three projections is checked before the first kernel is queued: a bad
+    // down operand must not leave the gate|up kernel running and the workspace half written.
+    rc = check_affine_ptrs(x, gate_w, gate_scales, gate_biases, out);
+    if (rc == MT_OK) rc = check_affine_ptrs(x, up_w, up_scales, up_biases, out);
+    if (rc == MT_OK) rc = check_affine_ptrs(workspace, down_w, down_scales, down_biases, out);
+    if (rc != MT_OK) return rc;
+    if ((flags & MT_FLAG_FORCE_GEMV) && M > 8) return MT_ERR_SHAPE;
+    if ((flags & MT_FLAG_UMMA_SCALED) && M > 16) return MT_ERR_SHAPE;
+    if ((flags & MT_FLAG_STREAM) && M > kStreamMaxRows) return MT_ERR_SHAPE;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
     // A handful of rows: the whole MLP as one cooperative launch when the shape fits it.  Any flag
     // that pins a kernel family keeps the two-kernel path; MT_FLAG_MLP_FUSED insists on this one.
     if (flags == 0 || (flags & (MT_FLAG_MLP_FUSED | MT_FLAG_MLP_FUSED_MMA))) {
@@ -271,7 +320,6 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
         params.hidden = static_cast<uint16_t*>(workspace);
         params.out = static_cast<uint16_t*>(out);
         params.barrier = nullptr;
-        params.timeline = g_timeline_buffer;
         params.M = M;
         params.H = H;
         params.I = I;
@@ -306,6 +354,16 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
     if (M < 0 || H < 1) return MT_ERR_SHAPE;
     if (M == 0) return MT_OK;
     if (!x_host || !out_host || !x_device || !out_device || (residual_host && !residual_device)) return MT_ERR_NULL;
+    // The MLP's own checks, made here before the first copy is queued.
+    int rc_early = check_format(H, I, group_size, bits);
+    if (rc_early == MT_OK) rc_early = check_format(I, H, group_size, bits);
+    if (rc_early != MT_OK) return rc_early;
+    if (!workspace || !aligned_to(workspace, 16) || workspace_bytes < mt_affine_mlp_workspace_bytes(M, H, I))
+        return MT_ERR_WORKSPACE;
+    rc_early = check_affine_ptrs(x_device, gate_w, gate_scales, gate_biases, out_device);
+    if (rc_early == MT_OK) rc_early = check_affine_ptrs(x_device, up_w, up_scales, up_biases, out_device);
+    if (rc_early == MT_OK) rc_early = check_affine_ptrs(workspace, down_w, down_scales, down_biases, out_device);
+    if (rc_early != MT_OK) return rc_early;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t bytes = (size_t)M * (size_t)H * 2;
     // Small copies cost their fixed latency, not their bytes: when the residual follows the activations

@@ -69,9 +69,10 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
     return done != 0;
 }
 
-// Bounded wait.  `abort_flag` lives in shared memory and is shared by the whole CTA.
+// Bounded wait.  `abort_flag` lives in shared memory and is shared by the whole CTA.  The kernels use
+// the 2 s limit; only the library's self-test passes a shorter one, through the same code.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned int code) {
+                                          unsigned int code, unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     for (int spin = 0; spin < 64; ++spin)
         if (mbar_try_wait_hint(bar, parity, 100000u)) return true;
@@ -79,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     while (true) {
         if (mbar_try_wait_hint(bar, parity, 100000u)) return true;
         if (*abort_flag) return false;
-        if (global_timer_ns() - start > kWaitLimitNs) {
+        if (global_timer_ns() - start > limit_ns) {
             if (atomicCAS(&g_device_status[0], 0u, code) == 0u) {
                 g_device_status[1] = blockIdx.x;
                 g_device_status[2] = threadIdx.x;
@@ -137,6 +138,16 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint3
 
 __device__ __forceinline__ void prefetch_tensor_map(const void* tensor_map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
+}
+
+// ---- cp.async: 16 bytes global -> shared through L2 (no L1 allocation), per-thread completion groups
+__device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait_group() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
 // ---- tcgen05 -----------------------------------------------------------------------------

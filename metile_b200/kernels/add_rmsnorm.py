@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes
 
 from .. import _lib
-from ..backends._common import library, pointer, require_cuda_bf16, stream_pointer
+from ..backends._common import launch, library, pointer, require_cuda_bf16, require_on_device
 
 
 def add_rmsnorm(X, Residual, W, Sum, Out, N, eps, BLOCK=256):
@@ -23,8 +23,9 @@ def add_rmsnorm(X, Residual, W, Sum, Out, N, eps, BLOCK=256):
     for tensor in (X, Residual, W, Sum, Out):
         if not tensor.is_contiguous():
             raise ValueError("add_rmsnorm expects contiguous tensors")
-    code = library().mt_add_rmsnorm(pointer(X), pointer(Residual), pointer(W), pointer(Sum),
-                                    pointer(Out), X.numel() // N, N, ctypes.c_float(float(eps)),
-                                    stream_pointer(X.device))
+    for label, tensor in (("Residual", Residual), ("W", W), ("Sum", Sum), ("Out", Out)):
+        require_on_device(tensor, X, label, dtype=X.dtype)
+    code = launch(library().mt_add_rmsnorm, X.device, pointer(X), pointer(Residual), pointer(W), pointer(Sum),
+                  pointer(Out), X.numel() // N, N, ctypes.c_float(float(eps)))
     _lib.check(code, "add_rmsnorm")
     return Sum, Out

@@ -12,10 +12,11 @@ from __future__ import annotations
 from .. import _lib
 from ..backends._common import (
     check_affine_triple,
+    launch,
     library,
     pointer,
     require_cuda_bf16,
-    stream_pointer,
+    require_on_device,
 )
 from ..backends.cuda_quantized import _flags
 
@@ -29,6 +30,7 @@ def _check_io(X, Out, K, N):
         raise ValueError("Out must be a contiguous [rows, N] tensor of the activation dtype")
     if not X.is_contiguous():
         raise ValueError("X must be contiguous")
+    require_on_device(Out, X, "Out", dtype=X.dtype, min_numel=rows * N)
     return rows
 
 
@@ -38,9 +40,8 @@ def affine_qmv(X, W, Scales, Biases, Out, K, N, GROUP_SIZE=64, BITS=4, BLOCK=32,
     rows = _check_io(X, Out, K, N)
     if check_affine_triple("affine_qmv", X, W, Scales, Biases, GROUP_SIZE, BITS) != N:
         raise ValueError("W does not have N rows")
-    code = library().mt_affine_qmv(pointer(X), pointer(W), pointer(Scales), pointer(Biases), None,
-                                   pointer(Out), rows, K, N, GROUP_SIZE, BITS, _flags(),
-                                   stream_pointer(X.device))
+    code = launch(library().mt_affine_qmv, X.device, pointer(X), pointer(W), pointer(Scales), pointer(Biases), None,
+                  pointer(Out), rows, K, N, GROUP_SIZE, BITS, _flags())
     _lib.check(code, "affine_qmv")
     return Out
 
@@ -53,9 +54,9 @@ def affine_residual_qmv(X, W, Scales, Biases, Residual, Out, K, N, GROUP_SIZE=64
         raise ValueError("W does not have N rows")
     if Residual.numel() != rows * N or Residual.dtype != X.dtype or not Residual.is_contiguous():
         raise ValueError("Residual must be a contiguous [rows, N] tensor of the activation dtype")
-    code = library().mt_affine_qmv(pointer(X), pointer(W), pointer(Scales), pointer(Biases),
-                                   pointer(Residual), pointer(Out), rows, K, N, GROUP_SIZE, BITS,
-                                   _flags(), stream_pointer(X.device))
+    require_on_device(Residual, X, "Residual", dtype=X.dtype, min_numel=rows * N)
+    code = launch(library().mt_affine_qmv, X.device, pointer(X), pointer(W), pointer(Scales), pointer(Biases),
+                  pointer(Residual), pointer(Out), rows, K, N, GROUP_SIZE, BITS, _flags())
     _lib.check(code, "affine_residual_qmv")
     return Out
 
@@ -69,10 +70,9 @@ def affine_swiglu_qmv(X, GateW, GateScales, GateBiases, UpW, UpScales, UpBiases,
         raise ValueError("GateW does not have N rows")
     if check_affine_triple("affine_swiglu_qmv", X, UpW, UpScales, UpBiases, GROUP_SIZE, BITS) != N:
         raise ValueError("UpW does not have N rows")
-    code = library().mt_affine_swiglu(pointer(X), pointer(GateW), pointer(GateScales),
-                                      pointer(GateBiases), pointer(UpW), pointer(UpScales),
-                                      pointer(UpBiases), pointer(Out), rows, K, N, GROUP_SIZE, BITS,
-                                      _flags(), stream_pointer(X.device))
+    code = launch(library().mt_affine_swiglu, X.device, pointer(X), pointer(GateW), pointer(GateScales),
+                  pointer(GateBiases), pointer(UpW), pointer(UpScales), pointer(UpBiases), pointer(Out), rows, K, N,
+                  GROUP_SIZE, BITS, _flags())
     _lib.check(code, "affine_swiglu_qmv")
     return Out
 

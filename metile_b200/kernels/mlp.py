@@ -14,10 +14,11 @@ from __future__ import annotations
 from .. import _lib
 from ..backends._common import (
     check_affine_triple,
+    launch,
     library,
     pointer,
     require_cuda_bf16,
-    stream_pointer,
+    require_on_device,
 )
 from ..backends.cuda_quantized import _flags
 
@@ -33,8 +34,9 @@ def _matmul_act(name, A, B, C, M, N, K, flags):
     for tensor in (A, B, C):
         if not tensor.is_contiguous():
             raise ValueError(f"{name} expects contiguous tensors")
-    code = library().mt_dense_act(pointer(A), pointer(B), pointer(C), M, N, K, flags,
-                                  stream_pointer(A.device))
+    require_on_device(B, A, "B", dtype=A.dtype, min_numel=K * N)
+    require_on_device(C, A, "C", dtype=A.dtype, min_numel=M * N)
+    code = launch(library().mt_dense_act, A.device, pointer(A), pointer(B), pointer(C), M, N, K, flags)
     _lib.check(code, name)
     return C
 
@@ -68,10 +70,15 @@ def affine_swiglu_mlp(X, GateW, GateScales, GateBiases, UpW, UpScales, UpBiases,
     for tensor in (X, Hidden, Out) + (() if Residual is None else (Residual,)):
         if not tensor.is_contiguous():
             raise ValueError(f"{name} expects contiguous tensors")
-    code = library().mt_affine_mlp(
-        pointer(X), pointer(GateW), pointer(GateScales), pointer(GateBiases), pointer(UpW),
-        pointer(UpScales), pointer(UpBiases), pointer(DownW), pointer(DownScales),
+    require_on_device(Hidden, X, "Hidden", dtype=X.dtype, min_numel=rows * intermediate)
+    require_on_device(Out, X, "Out", dtype=X.dtype, min_numel=rows * hidden_features)
+    require_on_device(Residual, X, "Residual", dtype=X.dtype, min_numel=rows * hidden_features)
+    if Residual is not None and Residual.numel() != rows * hidden_features:
+        raise ValueError("Residual must be a [rows, hidden] tensor")
+    code = launch(
+        library().mt_affine_mlp, X.device, pointer(X), pointer(GateW), pointer(GateScales), pointer(GateBiases),
+        pointer(UpW), pointer(UpScales), pointer(UpBiases), pointer(DownW), pointer(DownScales),
         pointer(DownBiases), pointer(Residual), pointer(Hidden), Hidden.numel() * 2, pointer(Out),
-        rows, hidden_features, intermediate, GROUP_SIZE, BITS, _flags(), stream_pointer(X.device))
+        rows, hidden_features, intermediate, GROUP_SIZE, BITS, _flags())
     _lib.check(code, name)
     return Out

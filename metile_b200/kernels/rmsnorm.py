@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 
 from .. import _lib
-from ..backends._common import library, pointer, require_cuda_bf16, stream_pointer
+from ..backends._common import launch, library, pointer, require_cuda_bf16, require_on_device
 
 
 def rmsnorm(X, W, Out, N, eps, BLOCK=256):
@@ -19,7 +19,9 @@ def rmsnorm(X, W, Out, N, eps, BLOCK=256):
     for tensor in (X, W, Out):
         if not tensor.is_contiguous():
             raise ValueError("rmsnorm expects contiguous tensors")
-    code = library().mt_rmsnorm(pointer(X), pointer(W), pointer(Out), X.numel() // N, N,
-                                ctypes.c_float(float(eps)), stream_pointer(X.device))
+    for label, tensor in (("W", W), ("Out", Out)):
+        require_on_device(tensor, X, label, dtype=X.dtype)
+    code = launch(library().mt_rmsnorm, X.device, pointer(X), pointer(W), pointer(Out), X.numel() // N, N,
+                  ctypes.c_float(float(eps)))
     _lib.check(code, "rmsnorm")
     return Out
