@@ -618,7 +618,7 @@ def main():
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--capture", default=None, metavar="OP:FAMILY:ROWS",
                         help="run a few launches of one operator and exit (a small target for ncu): OP is mlp, "
-                             "swiglu or down; FAMILY is default, mlp_fused, gemv, umma, umma_smem or umma_scaled")
+                             "swiglu or down; FAMILY is default, mlp_fused, mlp_fused_mma, gemv or umma")
     args = parser.parse_args()
     if args.capture:
         return run_capture(args.capture)

@@ -1,8 +1,11 @@
 /*
  * C ABI of libmetile_b200.so: the MLX-format affine INT4 projection path for NVIDIA B200
  * (sm_100a).  Plain pointers and sizes only; every pointer is DEVICE memory owned by the
- * caller; the library allocates nothing, keeps no pointer after a call returns, and every
- * call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream).
+ * caller; the library allocates no device memory, keeps no caller pointer after a call returns, and
+ * every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream).
+ * Every pointer and the stream must belong to the CURRENT device: the library takes its SM count, its
+ * per-device caches and its launches from it.  What the library does hold on each device is a few
+ * hundred bytes of status words and barrier counters, and the 4 MiB array of mt_affine_mlp_static.
  *
  * Data layout (identical to what the reference project consumes, so packed MLX weights drop
  * in unchanged -- metile/backends/mlx_quantized.py:478-480, kernels/affine_qmv.py:25-51):
@@ -15,27 +18,24 @@
  * Return value: 0 (MT_OK) or a negative code; mt_status_string() names it.  Codes:
  *   -1 shape, -2 alignment, -3 quantisation format, -4 CUDA launch error, -5 wrong device,
  *   -6 null pointer, -7 workspace, -8 a bounded device-side wait gave up.
- * Errors are detected before any GPU work is queued.  There is no CPU fallback.
+ * Argument errors (codes -1, -2, -3, -5, -6, -7) are detected before any GPU work is queued; -4 is
+ * what the CUDA runtime reported for a launch.  There is no CPU fallback.
  *
- * `flags`: 0 selects the kernel by row count (CUDA-core GEMV for M = 1, tcgen05 MMA above;
- * mt_affine_mlp with M <= 8 runs as one launch when the shape allows, see MT_FLAG_MLP_FUSED and
- * MT_FLAG_MLP_FUSED_MMA).
+ * `flags`: 0 selects the kernel by row count.  A single projection (mt_affine_qmv, mt_affine_swiglu):
+ * the CUDA-core GEMV for M = 1, the tcgen05 kernel above.  mt_affine_mlp: one cooperative launch for
+ * the whole MLP when the shape allows it -- on CUDA cores for M = 1 (H and I in {1024, 2048, 4096,
+ * 8192}), on mma.sync for M = 2 ... 8 (H in {512, 1024, 1536, 2048}, I a multiple of 512) -- else two
+ * kernels (gate|up SwiGLU, then down) of the families above.
  *   MT_FLAG_FORCE_GEMV (1)   CUDA-core GEMV (M <= 8)
- *   MT_FLAG_FORCE_UMMA (2)   tcgen05 path for any M (one accumulation order for every M:
- *                            use it when rows must be bit-identical across batch sizes 1..128)
- *   MT_FLAG_UMMA_SMEM_A (4)  tcgen05 path with the dequantised tile staged in shared memory
- *                            instead of tensor memory
- *   MT_FLAG_UMMA_SCALED (8)  tcgen05 path for M <= 16 with exact weights: the tensor core sums
- *                            x * (128 + q) per group and the group's scale and bias are applied to
- *                            the partial sums in fp32
+ *   MT_FLAG_FORCE_UMMA (2)   tcgen05 kernel for any M (one accumulation order for every M: use it
+ *                            when rows must be bit-identical across batch sizes 1..128)
  *   MT_FLAG_GELU (16)        mt_dense_act: x/(1+exp(-1.702x)) instead of SiLU
- *   MT_FLAG_MLP_FUSED (32)   mt_affine_mlp: insist on the single-launch kernel (M <= 4, H and I in
- *                            {1024, 2048, 4096, 8192}); -1 when it does not apply.  With flags = 0
- *                            mt_affine_mlp uses it for M = 1 whenever it applies, and takes the
- *                            two-kernel path if the driver refuses the cooperative launch.
- *   MT_FLAG_MLP_FUSED_MMA (128) mt_affine_mlp: insist on the warp-MMA variant of the single-launch
- *                            kernel (M <= 8, H in {512, 1024, 1536, 2048}, I a multiple of 512); -1
- *                            when it does not apply.  With flags = 0 it serves M = 2 ... 8.
+ *   MT_FLAG_MLP_FUSED (32)   mt_affine_mlp: insist on the single-launch CUDA-core kernel (M <= 4); -1
+ *                            when it does not apply.  With flags = 0 the default dispatch falls back
+ *                            to the two-kernel path if the driver refuses the cooperative launch.
+ *   MT_FLAG_HOST_PAIR (64)   mt_affine_mlp_host: see there
+ *   MT_FLAG_MLP_FUSED_MMA (128) mt_affine_mlp: insist on the mma.sync single-launch kernel (M <= 8);
+ *                            -1 when it does not apply.
  */
 #ifndef METILE_B200_H
 #define METILE_B200_H
@@ -49,13 +49,10 @@ extern "C" {
 
 #define MT_FLAG_FORCE_GEMV 0x1u
 #define MT_FLAG_FORCE_UMMA 0x2u
-#define MT_FLAG_UMMA_SMEM_A 0x4u
-#define MT_FLAG_UMMA_SCALED 0x8u
 #define MT_FLAG_GELU 0x10u
 #define MT_FLAG_MLP_FUSED 0x20u
 #define MT_FLAG_HOST_PAIR 0x40u
 #define MT_FLAG_MLP_FUSED_MMA 0x80u
-#define MT_FLAG_STREAM 0x100u
 
 /* Library version (major*10000 + minor*100 + patch). */
 int mt_version(void);
@@ -172,6 +169,34 @@ int mt_add_rmsnorm(const void* x, const void* residual, const void* weight, void
  * Replaces: metile/backends/mlx.py:748 (mlx_rms_norm), kernels/rmsnorm.py:5. */
 int mt_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, float eps,
                void* stream);
+
+/* Decode attention: one query row per sequence and head over a KV cache,
+ *   out[b, h, :] = softmax(scale * q[b, h, :] . K[b, h / (Hq/Hkv), 0:n, :]) @ V[b, h / (Hq/Hkv), 0:n, :],
+ * fp32 accumulation, one rounding at the store.  q, out: bf16 [batch, q_heads, head_dim]; k_cache,
+ * v_cache: bf16 [batch, kv_heads, capacity, head_dim] (the [B, H, N, D] layout of the reference's
+ * decode kernel with room for `capacity` tokens per head); n = lengths[b] when `lengths` (int32
+ * [batch], device) is given, else `tokens`, which must also bound every lengths[b].  head_dim 64 or
+ * 128, q_heads a multiple of kv_heads, at most 8 query heads per KV head.  `workspace`: device scratch
+ * of mt_attention_decode_workspace_bytes() bytes (0 when tokens <= 128), 16-byte aligned.
+ * Replaces: kernels/attention.py:27 (attention_decode_kernel), metile/backends/mlx.py:718
+ * (mlx_attention_decode), behind the admission rule of metile/integrations/mlx_lm.py:3558. */
+size_t mt_attention_decode_workspace_bytes(int batch, int q_heads, int tokens, int head_dim);
+int mt_attention_decode(const void* q, const void* k_cache, const void* v_cache, const int* lengths,
+                        void* out, void* workspace, size_t workspace_bytes, int batch, int q_heads,
+                        int kv_heads, int tokens, int capacity, int head_dim, float scale, void* stream);
+
+/* Rotary embedding of the new query and key rows (half-split pairs (i, i + D/2), angle =
+ * positions[b] * theta^(-2i/D)) and the in-place append of the rotated key and of the value at
+ * row positions[b] of each sequence's cache.  q: bf16 [batch, q_heads, head_dim], k, v: bf16 [batch,
+ * kv_heads, head_dim], consecutive sequences `row_stride` elements apart in all three (q_heads *
+ * head_dim etc. for dense arrays; the width of a fused q|k|v projection row when q, k and v point
+ * into one); q_out: dense bf16 [batch, q_heads, head_dim]; caches as for mt_attention_decode;
+ * positions: int32 [batch] on the device, each < capacity.  The reference leaves both steps to MLX-LM (nn.RoPE,
+ * KVCache.update_and_fetch); they are here so that a decode step needs no framework op between the
+ * projections and the attention kernel. */
+int mt_rope_kv_append(const void* q, const void* k, const void* v, long long row_stride,
+                      const int* positions, void* q_out, void* k_cache, void* v_cache, int batch,
+                      int q_heads, int kv_heads, int capacity, int head_dim, float theta, void* stream);
 
 /* Dense bf16 small-batch projection, w [N, K] bf16: out = bf16(bf16(x @ w^T) + residual).
  * Every row is bit-identical to running it alone.  K % 128 == 0.  residual may be NULL.

@@ -14,13 +14,10 @@ LIBRARY_PATH = os.path.join(HERE, "csrc", "libmetile_b200.so")
 
 FLAG_FORCE_GEMV = 0x1
 FLAG_FORCE_UMMA = 0x2
-FLAG_UMMA_SMEM_A = 0x4
-FLAG_UMMA_SCALED = 0x8
 FLAG_MLP_FUSED = 0x20
 FLAG_HOST_PAIR = 0x40
 FLAG_MLP_FUSED_MMA = 0x80
 FLAG_GELU = 0x10
-FLAG_STREAM = 0x100
 
 _VALUE_ERRORS = {-1, -2, -3, -6, -7}
 
@@ -46,6 +43,9 @@ SIGNATURES = {
     "mt_affine_mlp_static": (_i, [_p] * 12 + [_i, _i, _i, _i, _i, _u, _p]),
     "mt_add_rmsnorm": (_i, [_p, _p, _p, _p, _p, _i, _i, _f, _p]),
     "mt_rmsnorm": (_i, [_p, _p, _p, _i, _i, _f, _p]),
+    "mt_attention_decode_workspace_bytes": (_z, [_i, _i, _i, _i]),
+    "mt_attention_decode": (_i, [_p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _i, _i, _i, _f, _p]),
+    "mt_rope_kv_append": (_i, [_p, _p, _p, ctypes.c_longlong, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]),
     "mt_dense_rows": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
     "mt_dense_swiglu": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
     "mt_dense_act": (_i, [_p, _p, _p, _i, _i, _i, _u, _p]),

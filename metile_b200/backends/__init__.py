@@ -1,6 +1,12 @@
 """CUDA backends: torch-tensor operator entry points with the reference's names and signatures."""
 
-from .cuda import mlx_add_rms_norm, mlx_rms_norm  # noqa: F401
+from .cuda import (  # noqa: F401
+    mlx_add_rms_norm,
+    mlx_attention_decode,
+    mlx_rms_norm,
+    rope_kv_append,
+    supports_attention_decode,
+)
 from .cuda_affine import MLXAffineWeight, mlx_affine_matmul  # noqa: F401
 from .cuda_dense import (  # noqa: F401
     mlx_dense_residual_qmv,

@@ -64,13 +64,11 @@ def batch_invariant(enabled=True):
 
 @contextlib.contextmanager
 def force_kernel(name):
-    """Pin the kernel family: "gemv", "umma" (A operand in tensor memory), "umma_smem",
-    "umma_scaled" (exact weights, up to 16 rows), "mlp_fused" / "mlp_fused_mma" (the
-    single-launch MLP on CUDA cores / on mma.sync; projections called on their own are unaffected) or None."""
+    """Pin the kernel family: "gemv" (CUDA cores, up to 8 rows), "umma" (tcgen05), "mlp_fused" /
+    "mlp_fused_mma" (the single-launch MLP on CUDA cores / on mma.sync; projections called on their
+    own are unaffected) or None (the default dispatch by row count)."""
     table = {None: 0, "gemv": _lib.FLAG_FORCE_GEMV, "umma": _lib.FLAG_FORCE_UMMA,
-             "umma_smem": _lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A,
-             "umma_scaled": _lib.FLAG_UMMA_SCALED, "stream": _lib.FLAG_STREAM, "mlp_fused": _lib.FLAG_MLP_FUSED,
-             "mlp_fused_mma": _lib.FLAG_MLP_FUSED_MMA}
+             "mlp_fused": _lib.FLAG_MLP_FUSED, "mlp_fused_mma": _lib.FLAG_MLP_FUSED_MMA}
     if name not in table:
         raise ValueError(f"unknown kernel family {name!r}")
     previous = _flags()
@@ -84,12 +82,8 @@ def force_kernel(name):
 def _algorithm(rows, flags):
     if flags & _lib.FLAG_FORCE_GEMV:
         return "gemv"
-    if flags & _lib.FLAG_STREAM:
-        return "stream"
-    if flags & _lib.FLAG_UMMA_SCALED:
-        return "umma_scaled"
-    if flags & (_lib.FLAG_FORCE_UMMA | _lib.FLAG_UMMA_SMEM_A):
-        return "umma_smem" if flags & _lib.FLAG_UMMA_SMEM_A else "umma"
+    if flags & _lib.FLAG_FORCE_UMMA:
+        return "umma"
     return "gemv" if rows <= 1 else "umma"
 
 

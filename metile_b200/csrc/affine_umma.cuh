@@ -22,8 +22,7 @@
 //                    One thread per weight row; nibbles -> bf16x2 in NATURAL element order (pairs
 //                    (e0,e1), (e2,e3), ...: two masks, one byte-permute and one or-with-0x4300 per
 //                    pair = 128+q), q = v-128, w = fma(q, scale, bias) (one rounding:
-//                    RN_bf16(scale*q+bias)); result either stored to TMEM as the A operand (kTmemA)
-//                    or to 128B-swizzled shared memory
+//                    RN_bf16(scale*q+bias)); result stored to tensor memory as the A operand
 //   x lane         : the activation tile of each k-block ([kMPad rows] x 64 columns, rows past M
 //                    zero-filled) arrives by TMA straight into the swizzled B tile: no thread touches
 //                    the activations, whose handling cost as many instructions as the dequantisation
@@ -55,15 +54,15 @@ constexpr int pow2_at_least(int v) {
     return p;
 }
 
-template <int kT, int kMPad, bool kTmemA>
+template <int kT, int kMPad>
 struct UmmaConfig {
     // One footprint: 16 dequant warps, one CTA per SM.  A lighter variant (8 dequant warps, two
     // CTAs per SM so that consecutive kernels chained by programmatic dependent launch overlap)
     // was measured and was slower (16.2 vs 12.7 us for the 2048->8192 gate|up projection at one
     // row): what limits a CTA is the latency of one warp's dequant iteration, so halving the
-    // warps per CTA doubled it and the overlap did not pay that back.
-    static constexpr bool kLight = false;
-    static constexpr int kDequantWarps = kLight ? 8 : 16;           // 4 warps x kT tiles x kDepth
+    // warps per CTA doubled it and the overlap did not pay that back.  Staging the dequantised A
+    // tile in shared memory instead of tensor memory was measured too and never won.
+    static constexpr int kDequantWarps = 16;                        // 4 warps x kT tiles x kDepth
     static constexpr int kDepth = kDequantWarps / (4 * kT);         // dequant groups per tile
     static constexpr int kWarpsPerKBlock = 4 * kT;                  // warps that serve one k-block
     static constexpr int kProducerWarp = kDequantWarps;
@@ -72,20 +71,18 @@ struct UmmaConfig {
     static constexpr int kThreads = (kDequantWarps + 3) * 32;
     static constexpr int kWTileBytes = kUmmaTileRows * 128;         // one packed tile, four k-blocks
     static constexpr int kSlotBytes = kT * kWTileBytes;
-    static constexpr int kATileBytes = kUmmaTileRows * 128;         // one dequantised bf16 tile, one k-block
-    static constexpr int kABytes = kTmemA ? 0 : kT * kATileBytes;
-    static constexpr int kBBytes = kMPad * 128;
-    static constexpr int kAbBytes = kABytes + kBBytes;
-    static constexpr int kAbStages = !kTmemA ? kDepth : (kLight && kT == 2 ? 3 : 4);
+    static constexpr int kBBytes = kMPad * 128;                     // activation tile of one k-block
+    static constexpr int kAbBytes = kBBytes;                        // operand bytes per stage in shared memory (A lives in tensor memory)
+    static constexpr int kAbStages = 4;
     // One accumulator per tile.  Measured on B200: a tcgen05.mma with M=128, K=16 costs ~45 cycles
     // for any N <= 64 (64 for N=128, 128 for N=256) whether or not consecutive instructions share an
     // accumulator, so splitting the K steps over several accumulators buys nothing.
     static constexpr int kAcc = 1;
     static constexpr int kAccCols = kT * kAcc * kMPad;
-    static constexpr int kATmemCols = kTmemA ? kAbStages * kT * 32 : 0;
+    static constexpr int kATmemCols = kAbStages * kT * 32;
     static constexpr int kTmemCols = pow2_at_least(kAccCols + kATmemCols);
     // The ring takes what shared memory the footprint leaves, up to 8 slots.
-    static constexpr int kBudgetBytes = (kLight ? 108 : 196) * 1024;
+    static constexpr int kBudgetBytes = 196 * 1024;
     static constexpr int kRingTarget = kBudgetBytes - kAbStages * kAbBytes;
     static constexpr int kStagesRaw = kRingTarget / kSlotBytes;
     static constexpr int kStages = kStagesRaw < 2 ? 2 : (kStagesRaw > 8 ? 8 : kStagesRaw);
@@ -96,7 +93,7 @@ struct UmmaConfig {
     // TMEM columns x resident CTAs must never exceed 512: a later CTA's tcgen05.alloc would wait
     // for an earlier CTA to finish.  Shared memory bounds residency, so every CTA asks for more
     // than 1/(allowed+1) of an SM's shared memory.
-    static constexpr int kAllowedPerSm = kLight ? 2 : 1;
+    static constexpr int kAllowedPerSm = 1;
     static constexpr int kFloorBytes = (227 * 1024) / (kAllowedPerSm + 1) + 2048;
     static constexpr int kDataBytes = kDataBytesMin < kFloorBytes ? kFloorBytes : kDataBytesMin;
     static constexpr int kBarrierBytes = 8 * (2 * kStages + 2 * kAbStages + 1) + 16;
@@ -168,10 +165,10 @@ __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
     return v;
 }
 
-template <int kT, int kMPad, bool kTmemA, bool kSwiglu>
-__global__ void __launch_bounds__(UmmaConfig<kT, kMPad, kTmemA>::kThreads, UmmaConfig<kT, kMPad, kTmemA>::kAllowedPerSm)
+template <int kT, int kMPad, bool kSwiglu>
+__global__ void __launch_bounds__(UmmaConfig<kT, kMPad>::kThreads, UmmaConfig<kT, kMPad>::kAllowedPerSm)
 affine_umma_kernel(const __grid_constant__ UmmaParams p) {
-    using Cfg = UmmaConfig<kT, kMPad, kTmemA>;
+    using Cfg = UmmaConfig<kT, kMPad>;
     static_assert(!kSwiglu || kT == 2, "SwiGLU pairs a gate tile with an up tile");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -264,7 +261,7 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 const uint32_t phase = (uint32_t)(i / Cfg::kAbStages) & 1u;
                 if (!ptx::mbar_wait(&ab_empty[a], phase ^ 1u, abort_flag, kWaitAbEmpty)) break;
                 ptx::mbar_expect_tx(&ab_full[a], Cfg::kBBytes);
-                ptx::tma_load_2d(ab + a * Cfg::kAbBytes + Cfg::kABytes, &p.x_map, (kb_begin + i) * kUmmaBlockK, 0,
+                ptx::tma_load_2d(ab + a * Cfg::kAbBytes, &p.x_map, (kb_begin + i) * kUmmaBlockK, 0,
                                  &ab_full[a]);
                 ++issued;
             }
@@ -301,16 +298,10 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                             const int chain = ks % Cfg::kAcc;
                             const uint32_t d_tmem = tmem_base + (t * Cfg::kAcc + chain) * kMPad;
                             const uint64_t b_desc =
-                                desc0 + (uint64_t)((a * Cfg::kAbBytes + Cfg::kABytes + ks * 32) >> 4);
+                                desc0 + (uint64_t)((a * Cfg::kAbBytes + ks * 32) >> 4);
                             const uint32_t accumulate = (a > 0 || ks >= Cfg::kAcc) ? 1u : later;
-                            if constexpr (kTmemA) {
-                                const uint32_t a_tmem = tmem_base + Cfg::kAccCols + (a * kT + t) * 32 + ks * 8;
-                                ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
-                            } else {
-                                const uint64_t a_desc =
-                                    desc0 + (uint64_t)((a * Cfg::kAbBytes + t * Cfg::kATileBytes + ks * 32) >> 4);
-                                ptx::umma_ss(d_tmem, a_desc, b_desc, idesc, accumulate);
-                            }
+                            const uint32_t a_tmem = tmem_base + Cfg::kAccCols + (a * kT + t) * 32 + ks * 8;
+                            ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
                         }
                     }
                     ptx::umma_commit(&ab_empty[a]);
@@ -369,28 +360,16 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
 #pragma unroll
                 for (int c = 0; c < 8; ++c) dequant_word_bf16(words[c], scale2, bias2, &wq[4 * c]);
 
-                [[maybe_unused]] uint8_t* ab_stage = ab + a * Cfg::kAbBytes;
-                if constexpr (kTmemA) {
-                    const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + Cfg::kAccCols +
-                                            (a * kT + t) * 32;
-                    ptx::tmem_st16(a_tmem, &wq[0]);
-                    ptx::tmem_st16(a_tmem + 16, &wq[16]);
-                } else {
-                    uint8_t* a_row = ab_stage + t * Cfg::kATileBytes + r * 128;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4*>(a_row + ((c ^ (r & 7)) << 4)) =
-                            make_uint4(wq[4 * c], wq[4 * c + 1], wq[4 * c + 2], wq[4 * c + 3]);
-                }
-                // One cross-proxy fence covers both directions: an A tile written to shared memory above
-                // becomes visible to the MMA (async proxy), and the ring slot read above with ordinary
-                // loads may later be overwritten by TMA (async proxy).  Releasing a slot without such a
-                // fence was observed to let the refill overtake the reads.
+                const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + Cfg::kAccCols +
+                                        (a * kT + t) * 32;
+                ptx::tmem_st16(a_tmem, &wq[0]);
+                ptx::tmem_st16(a_tmem + 16, &wq[16]);
+                // The ring slot read above with ordinary loads may later be overwritten by TMA (async
+                // proxy): order the two.  Releasing a slot without such a fence was observed to let the
+                // refill overtake the reads.
                 ptx::fence_proxy_async_smem();
-                if constexpr (kTmemA) {
-                    ptx::tc_wait_st();
-                    ptx::tc_fence_before_sync();
-                }
+                ptx::tc_wait_st();
+                ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&ab_full[a]);
             }
@@ -566,14 +545,14 @@ inline bool encode_weight_map(CUtensorMap* map, const void* base, int K, int N, 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int kT, int kMPad, bool kTmemA, bool kSwiglu>
+template <int kT, int kMPad, bool kSwiglu>
 inline cudaError_t configure_umma_instance() {
-    using Cfg = UmmaConfig<kT, kMPad, kTmemA>;
+    using Cfg = UmmaConfig<kT, kMPad>;
     static bool configured[64] = {};
     int device = 0;
     cudaGetDevice(&device);
     if (device < 64 && configured[device]) return cudaSuccess;
-    const cudaError_t rc = cudaFuncSetAttribute(affine_umma_kernel<kT, kMPad, kTmemA, kSwiglu>,
+    const cudaError_t rc = cudaFuncSetAttribute(affine_umma_kernel<kT, kMPad, kSwiglu>,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (rc == cudaSuccess && device < 64) configured[device] = true;
     return rc;
@@ -582,14 +561,14 @@ inline cudaError_t configure_umma_instance() {
 // How many clusters of `size` CTAs of the 128-row instance can be resident at once.  Measured on
 // the largest instance of the family so that the answer, and with it the K split, does not depend
 // on the number of activation rows.
-template <int kT, bool kTmemA, bool kSwiglu>
+template <int kT, bool kSwiglu>
 inline int umma_active_clusters(int size) {
     static int cached[64][9] = {};
     int device = 0;
     cudaGetDevice(&device);
     if (device < 64 && cached[device][size]) return cached[device][size];
-    using Cfg = UmmaConfig<kT, 128, kTmemA>;
-    if (configure_umma_instance<kT, 128, kTmemA, kSwiglu>() != cudaSuccess) return 0;
+    using Cfg = UmmaConfig<kT, 128>;
+    if (configure_umma_instance<kT, 128, kSwiglu>() != cudaSuccess) return 0;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(size * 64, 1, 1);
     config.blockDim = dim3(Cfg::kThreads, 1, 1);
@@ -602,7 +581,7 @@ inline int umma_active_clusters(int size) {
     config.attrs = attrs;
     config.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, affine_umma_kernel<kT, 128, kTmemA, kSwiglu>, &config) !=
+    if (cudaOccupancyMaxActiveClusters(&clusters, affine_umma_kernel<kT, 128, kSwiglu>, &config) !=
         cudaSuccess)
         clusters = 0;
     if (device < 64) cached[device][size] = clusters > 0 ? clusters : -1;
@@ -611,13 +590,13 @@ inline int umma_active_clusters(int size) {
 
 // Cluster size along K.  A function of (tile count, K, kernel family, device) only -- never of the
 // number of activation rows.  cost = waves x (ring slots per CTA + a fixed prologue/epilogue term).
-template <int kT, bool kTmemA, bool kSwiglu>
+template <int kT, bool kSwiglu>
 inline int umma_ksplit(int tiles, int slots_total) {
     int best = 1;
     long best_cost = -1;
     for (int s = 1; s <= 8; ++s) {
         if (s > slots_total) break;
-        const int active = umma_active_clusters<kT, kTmemA, kSwiglu>(s);
+        const int active = umma_active_clusters<kT, kSwiglu>(s);
         if (active <= 0) continue;
         const long waves = (tiles + active - 1) / active;
         const long per_cta = (slots_total + s - 1) / s;
@@ -630,10 +609,10 @@ inline int umma_ksplit(int tiles, int slots_total) {
     return best;
 }
 
-template <int kT, int kMPad, bool kTmemA, bool kSwiglu>
+template <int kT, int kMPad, bool kSwiglu>
 inline int launch_umma_instance(const UmmaParams& params, int tiles, cudaStream_t stream) {
-    using Cfg = UmmaConfig<kT, kMPad, kTmemA>;
-    if (configure_umma_instance<kT, kMPad, kTmemA, kSwiglu>() != cudaSuccess) return MT_ERR_LAUNCH;
+    using Cfg = UmmaConfig<kT, kMPad>;
+    if (configure_umma_instance<kT, kMPad, kSwiglu>() != cudaSuccess) return MT_ERR_LAUNCH;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(tiles * params.ksplit, 1, 1);
     config.blockDim = dim3(Cfg::kThreads, 1, 1);
@@ -648,20 +627,20 @@ inline int launch_umma_instance(const UmmaParams& params, int tiles, cudaStream_
     attrs[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attrs;
     config.numAttrs = 2;
-    return cudaLaunchKernelEx(&config, affine_umma_kernel<kT, kMPad, kTmemA, kSwiglu>, params) == cudaSuccess
+    return cudaLaunchKernelEx(&config, affine_umma_kernel<kT, kMPad, kSwiglu>, params) == cudaSuccess
                ? MT_OK
                : MT_ERR_LAUNCH;
 }
 
-template <int kT, bool kTmemA, bool kSwiglu>
+template <int kT, bool kSwiglu>
 inline int launch_umma_family(UmmaParams& params, int tiles, int mpad, cudaStream_t stream) {
     const int kblocks = params.K / kUmmaBlockK;
-    params.ksplit = umma_ksplit<kT, kTmemA, kSwiglu>(tiles, (kblocks + kUmmaKBlocksPerSlot - 1) / kUmmaKBlocksPerSlot);
+    params.ksplit = umma_ksplit<kT, kSwiglu>(tiles, (kblocks + kUmmaKBlocksPerSlot - 1) / kUmmaKBlocksPerSlot);
     switch (mpad) {
-        case 16: return launch_umma_instance<kT, 16, kTmemA, kSwiglu>(params, tiles, stream);
-        case 32: return launch_umma_instance<kT, 32, kTmemA, kSwiglu>(params, tiles, stream);
-        case 64: return launch_umma_instance<kT, 64, kTmemA, kSwiglu>(params, tiles, stream);
-        case 128: return launch_umma_instance<kT, 128, kTmemA, kSwiglu>(params, tiles, stream);
+        case 16: return launch_umma_instance<kT, 16, kSwiglu>(params, tiles, stream);
+        case 32: return launch_umma_instance<kT, 32, kSwiglu>(params, tiles, stream);
+        case 64: return launch_umma_instance<kT, 64, kSwiglu>(params, tiles, stream);
+        case 128: return launch_umma_instance<kT, 128, kSwiglu>(params, tiles, stream);
         default: return MT_ERR_SHAPE;
     }
 }
@@ -674,7 +653,7 @@ struct AffineWeights {
 
 // x [M,K] bf16 (M <= 128), one weight triple (plain / residual) or two (gate, up -> SwiGLU).
 inline int launch_umma(const void* x, const AffineWeights* first, const AffineWeights* second, const void* residual,
-                       void* out, int M, int K, int N, bool tmem_a, cudaStream_t stream) {
+                       void* out, int M, int K, int N, cudaStream_t stream) {
     if (M < 1 || M > 128 || K % kUmmaBlockK || K < kUmmaBlockK || N < 1) return MT_ERR_SHAPE;
     if (!aligned_to(x, 16) || !aligned_to(first->w, 16) || (second && !aligned_to(second->w, 16))) return MT_ERR_ALIGN;
     const bool swiglu = second != nullptr;
@@ -695,12 +674,8 @@ inline int launch_umma(const void* x, const AffineWeights* first, const AffineWe
     if (!encode_weight_map(&params.w_map[0], first->w, K, N)) return MT_ERR_LAUNCH;
     if (!encode_weight_map(&params.w_map[1], swiglu ? second->w : first->w, K, N)) return MT_ERR_LAUNCH;
     if (!encode_activation_map(&params.x_map, x, M, K, mpad)) return MT_ERR_LAUNCH;
-    if (swiglu) {
-        return tmem_a ? launch_umma_family<2, true, true>(params, tiles, mpad, stream)
-                      : launch_umma_family<2, false, true>(params, tiles, mpad, stream);
-    }
-    return tmem_a ? launch_umma_family<1, true, false>(params, tiles, mpad, stream)
-                  : launch_umma_family<1, false, false>(params, tiles, mpad, stream);
+    return swiglu ? launch_umma_family<2, true>(params, tiles, mpad, stream)
+                  : launch_umma_family<1, false>(params, tiles, mpad, stream);
 }
 
 }  // namespace mt

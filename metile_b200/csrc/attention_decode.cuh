@@ -44,8 +44,6 @@ struct AttentionParams {
     float scale;
 };
 
-__device__ __forceinline__ uint4 ld_global_dependent_nc_free(const void* p) { return ptx::ld_global_dependent_u4(p); }
-
 template <int kD, int kG>
 __global__ void __launch_bounds__(128) attention_decode_split_kernel(const AttentionParams p) {
     constexpr int kPerLane = kD / 32;  // head-dim elements a lane owns in the value phase (2 or 4)
@@ -251,14 +249,15 @@ inline int launch_attention_dim(const AttentionParams& params, int batch, int gr
 // query and key rows, and the append of the rotated key and of the value at `position` of each
 // sequence's cache.  One CTA per (sequence, head) over Hq + 2 Hkv heads; thread i owns pair i.
 struct RopeAppendParams {
-    const uint16_t* q;        // [B, Hq, D]
-    const uint16_t* k;        // [B, Hkv, D]
-    const uint16_t* v;        // [B, Hkv, D]
+    const uint16_t* q;        // [B, Hq, D], consecutive sequences `row_stride` elements apart
+    const uint16_t* k;        // [B, Hkv, D], same stride
+    const uint16_t* v;        // [B, Hkv, D], same stride
     const int* positions;     // [B]
     uint16_t* q_out;          // [B, Hq, D]
     uint16_t* k_cache;        // [B, Hkv, capacity, D]
     uint16_t* v_cache;
     int q_heads, kv_heads, capacity, head_dim;
+    long long row_stride;     // elements between sequences in q, k and v (one fused q|k|v row, or dense)
     float log2_theta;
 };
 
@@ -271,14 +270,14 @@ __global__ void rope_kv_append_kernel(const RopeAppendParams p) {
     const int position = p.positions[b];
     if (slot >= p.q_heads + p.kv_heads) {  // value row: a plain copy into the cache
         const int h = slot - p.q_heads - p.kv_heads;
-        const uint16_t* from = p.v + ((size_t)b * p.kv_heads + h) * dim;
+        const uint16_t* from = p.v + (size_t)b * p.row_stride + (size_t)h * dim;
         uint16_t* to = p.v_cache + (((size_t)b * p.kv_heads + h) * p.capacity + position) * dim;
         for (int d = threadIdx.x; d < dim; d += blockDim.x) to[d] = ptx::ld_global_dependent_u16(from + d);
         return;
     }
     const bool is_query = slot < p.q_heads;
     const int h = is_query ? slot : slot - p.q_heads;
-    const uint16_t* from = is_query ? p.q + ((size_t)b * p.q_heads + h) * dim : p.k + ((size_t)b * p.kv_heads + h) * dim;
+    const uint16_t* from = (is_query ? p.q : p.k) + (size_t)b * p.row_stride + (size_t)h * dim;
     uint16_t* to = is_query ? p.q_out + ((size_t)b * p.q_heads + h) * dim
                             : p.k_cache + (((size_t)b * p.kv_heads + h) * p.capacity + position) * dim;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {

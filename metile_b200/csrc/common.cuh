@@ -19,12 +19,9 @@
 // ---- flags word ---------------------------------------------------------------------------
 #define MT_FLAG_FORCE_GEMV 0x1u   // CUDA-core GEMV regardless of row count (rows <= 8 only)
 #define MT_FLAG_FORCE_UMMA 0x2u   // tcgen05 path regardless of row count
-#define MT_FLAG_UMMA_SMEM_A 0x4u  // tcgen05 path with the dequantised tile staged in shared memory
-#define MT_FLAG_UMMA_SCALED 0x8u   // tcgen05 path, <= 16 rows, scale and bias applied to group partial sums
 #define MT_FLAG_MLP_FUSED_MMA 0x80u  // mt_affine_mlp: insist on the warp-MMA single-launch kernel (M <= 8)
 #define MT_FLAG_HOST_PAIR 0x40u    // mt_affine_mlp_host: activations and residual share one host allocation
 #define MT_FLAG_MLP_FUSED 0x20u    // mt_affine_mlp: insist on the single-launch kernel (error if it does not apply)
-#define MT_FLAG_STREAM 0x100u     // half-SM tcgen05 kernel with exact weights (rows <= 32)
 #define MT_FLAG_GELU 0x10u        // dense activation: x/(1+exp(-1.702x)) instead of SiLU
 
 namespace mt {

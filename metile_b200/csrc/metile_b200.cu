@@ -3,11 +3,10 @@
 #include "../../include/metile_b200.h"
 
 #include "add_rmsnorm.cuh"
+#include "attention_decode.cuh"
 #include "affine_gemv.cuh"
 #include "affine_umma.cuh"
 #include "affine_mlp_fused.cuh"
-#include "affine_umma_scaled.cuh"
-#include "affine_stream.cuh"
 #include "common.cuh"
 #include "dense_rows.cuh"
 
@@ -53,7 +52,7 @@ static int check_affine_ptrs(const void* x, const uint32_t* w, const void* s, co
 // Llama-3.2-1B shape: 18.7 us vs 24.6 us) and loses from two rows on (26.1 us vs 24.7 us).
 static bool use_gemv(int M, unsigned int flags) {
     if (flags & MT_FLAG_FORCE_GEMV) return true;
-    if (flags & (MT_FLAG_FORCE_UMMA | MT_FLAG_UMMA_SMEM_A | MT_FLAG_UMMA_SCALED | MT_FLAG_STREAM)) return false;
+    if (flags & MT_FLAG_FORCE_UMMA) return false;
     return M <= 1;
 }
 
@@ -69,22 +68,13 @@ static int run_projection(const void* x, const AffineWeights& first, const Affin
         return second ? launch_gemv<true>(x, a, b, residual, out, M, K, N, sms, stream)
                       : launch_gemv<false>(x, a, b, residual, out, M, K, N, sms, stream);
     }
-    if (flags & MT_FLAG_STREAM) {
-        if (M > kStreamMaxRows) return MT_ERR_SHAPE;
-        return launch_stream(x, &first, second, residual, out, M, K, N, sms, stream);
-    }
-    if (flags & MT_FLAG_UMMA_SCALED) {
-        if (M > 16) return MT_ERR_SHAPE;
-        return launch_umma_scaled_any(x, &first, second, residual, out, M, K, N, stream);
-    }
-    const bool tmem_a = !(flags & MT_FLAG_UMMA_SMEM_A);
     const uint16_t* xp = static_cast<const uint16_t*>(x);
     const uint16_t* rp = static_cast<const uint16_t*>(residual);
     uint16_t* op = static_cast<uint16_t*>(out);
     for (int m0 = 0; m0 < M; m0 += 128) {
         const int rows = M - m0 < 128 ? M - m0 : 128;
         const int rc = launch_umma(xp + (size_t)m0 * K, &first, second, rp ? rp + (size_t)m0 * N : nullptr,
-                                   op + (size_t)m0 * N, rows, K, N, tmem_a, stream);
+                                   op + (size_t)m0 * N, rows, K, N, stream);
         if (rc != MT_OK) return rc;
     }
     return MT_OK;
@@ -295,8 +285,6 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
     if (rc == MT_OK) rc = check_affine_ptrs(workspace, down_w, down_scales, down_biases, out);
     if (rc != MT_OK) return rc;
     if ((flags & MT_FLAG_FORCE_GEMV) && M > 8) return MT_ERR_SHAPE;
-    if ((flags & MT_FLAG_UMMA_SCALED) && M > 16) return MT_ERR_SHAPE;
-    if ((flags & MT_FLAG_STREAM) && M > kStreamMaxRows) return MT_ERR_SHAPE;
     if (!device_is_sm100()) return MT_ERR_DEVICE;
     // A handful of rows: the whole MLP as one cooperative launch when the shape fits it.  Any flag
     // that pins a kernel family keeps the two-kernel path; MT_FLAG_MLP_FUSED insists on this one.
@@ -431,6 +419,80 @@ int mt_rmsnorm(const void* x, const void* weight, void* out, int rows, int H, fl
     if (rows == 0) return MT_OK;
     if (!device_is_sm100()) return MT_ERR_DEVICE;
     return launch_add_rmsnorm(x, nullptr, weight, nullptr, out, rows, H, eps, static_cast<cudaStream_t>(stream));
+}
+
+size_t mt_attention_decode_workspace_bytes(int batch, int q_heads, int tokens, int head_dim) {
+    if (batch <= 0 || q_heads <= 0 || tokens <= 0 || head_dim <= 0) return 0;
+    return attention_workspace_bytes(batch, q_heads, tokens, head_dim);
+}
+
+int mt_attention_decode(const void* q, const void* k_cache, const void* v_cache, const int* lengths, void* out,
+                        void* workspace, size_t workspace_bytes, int batch, int q_heads, int kv_heads, int tokens,
+                        int capacity, int head_dim, float scale, void* stream) {
+    if (batch < 0 || q_heads < 1 || kv_heads < 1 || q_heads % kv_heads || q_heads / kv_heads > kAttnMaxGroup)
+        return MT_ERR_SHAPE;
+    if (head_dim != 64 && head_dim != 128) return MT_ERR_SHAPE;
+    if (tokens < 1 || capacity < tokens) return MT_ERR_SHAPE;
+    if (batch == 0) return MT_OK;
+    if (!q || !k_cache || !v_cache || !out) return MT_ERR_NULL;
+    if (!aligned_to(q, 16) || !aligned_to(k_cache, 16) || !aligned_to(v_cache, 16) || !aligned_to(out, 2))
+        return MT_ERR_ALIGN;
+    const int splits = attention_splits(tokens);
+    if (splits > 1 && (!workspace || !aligned_to(workspace, 16) ||
+                       workspace_bytes < attention_workspace_bytes(batch, q_heads, tokens, head_dim)))
+        return MT_ERR_WORKSPACE;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    AttentionParams params;
+    params.q = static_cast<const uint16_t*>(q);
+    params.k = static_cast<const uint16_t*>(k_cache);
+    params.v = static_cast<const uint16_t*>(v_cache);
+    params.lengths = lengths;
+    params.partial = static_cast<float*>(workspace);
+    params.out = static_cast<uint16_t*>(out);
+    params.q_heads = q_heads;
+    params.kv_heads = kv_heads;
+    params.capacity = capacity;
+    params.tokens = tokens;
+    params.splits = splits;
+    params.scale = scale;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return head_dim == 128 ? launch_attention_dim<128>(params, batch, q_heads / kv_heads, s)
+                           : launch_attention_dim<64>(params, batch, q_heads / kv_heads, s);
+}
+
+int mt_rope_kv_append(const void* q, const void* k, const void* v, long long row_stride, const int* positions,
+                      void* q_out, void* k_cache, void* v_cache, int batch, int q_heads, int kv_heads, int capacity,
+                      int head_dim, float theta, void* stream) {
+    if (batch < 0 || q_heads < 1 || kv_heads < 1 || capacity < 1 || head_dim < 2 || head_dim % 2 || theta <= 0.0f)
+        return MT_ERR_SHAPE;
+    if (row_stride < (long long)kv_heads * head_dim) return MT_ERR_SHAPE;
+    if (batch == 0) return MT_OK;
+    if (!q || !k || !v || !positions || !q_out || !k_cache || !v_cache) return MT_ERR_NULL;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    RopeAppendParams params;
+    params.q = static_cast<const uint16_t*>(q);
+    params.k = static_cast<const uint16_t*>(k);
+    params.v = static_cast<const uint16_t*>(v);
+    params.positions = positions;
+    params.q_out = static_cast<uint16_t*>(q_out);
+    params.k_cache = static_cast<uint16_t*>(k_cache);
+    params.v_cache = static_cast<uint16_t*>(v_cache);
+    params.q_heads = q_heads;
+    params.kv_heads = kv_heads;
+    params.capacity = capacity;
+    params.head_dim = head_dim;
+    params.row_stride = row_stride;
+    params.log2_theta = log2f(theta);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(batch * (q_heads + 2 * kv_heads), 1, 1);
+    config.blockDim = dim3(64, 1, 1);
+    config.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attrs;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, rope_kv_append_kernel, params) == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
 }
 
 int mt_dense_rows(const void* x, const void* w, const void* residual, void* out, int M, int K, int N, void* stream) {

@@ -81,40 +81,82 @@ class GatedMLP(nn.Module):
 
 
 def _rope(values, positions, theta):
-    """Rotary embedding over the last axis (half-split form); values [B, heads, T, D]."""
+    """Rotary embedding over the last axis (half-split form); values [B, heads, T, D], positions [T]
+    or [B, T]."""
     dim = values.shape[-1]
     inverse = 1.0 / (theta ** (torch.arange(0, dim, 2, device=values.device, dtype=torch.float32) / dim))
-    angles = positions.float()[:, None] * inverse[None, :]
-    cos, sin = angles.cos()[None, None], angles.sin()[None, None]
+    angles = positions.float()[..., None] * inverse
+    if angles.ndim == 2:
+        angles = angles[None]
+    cos, sin = angles.cos()[:, None], angles.sin()[:, None]
     first, second = values.float()[..., : dim // 2], values.float()[..., dim // 2:]
     return torch.cat([first * cos - second * sin, second * cos + first * sin], dim=-1).to(values.dtype)
 
 
+class KVCache:
+    """Append-only key/value cache with room for `capacity` tokens per head, updated in place.
+
+    The MLX-LM cache the reference's models use (`KVCache.update_and_fetch`) grows by concatenation;
+    here the storage is allocated once as [batch, kv_heads, capacity, head_dim] and a step writes its
+    rows at `length`, so a decode step moves only the new token's bytes."""
+
+    def __init__(self, batch, kv_heads, capacity, head_dim, device, dtype=torch.bfloat16):
+        self.keys = torch.zeros((batch, kv_heads, capacity, head_dim), dtype=dtype, device=device)
+        self.values = torch.zeros_like(self.keys)
+        self.length = 0
+        self.positions = torch.zeros((batch,), dtype=torch.int32, device=device)
+
+    @property
+    def capacity(self):
+        return self.keys.shape[2]
+
+    def update_and_fetch(self, keys, values):
+        """Write keys / values [B, H, T, D] at the current length; return views of all tokens so far."""
+        steps = keys.shape[2]
+        if self.length + steps > self.capacity:
+            raise ValueError("KV cache capacity exceeded")
+        self.keys[:, :, self.length:self.length + steps] = keys
+        self.values[:, :, self.length:self.length + steps] = values
+        self.advance(steps)
+        return self.keys[:, :, :self.length], self.values[:, :, :self.length]
+
+    def advance(self, steps=1):
+        self.length += steps
+        self.positions.fill_(self.length)
+
+
+def scaled_dot_product_attention(queries, keys, values, cache, scale, mask=None):
+    """The attention primitive every Attention module here calls; the patcher replaces THIS module
+    attribute (the reference replaces mlx_lm.models.base.scaled_dot_product_attention the same way,
+    metile/integrations/mlx_lm.py:4607-4655).  queries [B, Hq, T, D], keys / values [B, Hkv, N, D]."""
+    del cache
+    causal = mask == "causal"
+    return nn.functional.scaled_dot_product_attention(
+        queries, keys, values, scale=scale, is_causal=causal, enable_gqa=queries.shape[1] != keys.shape[1])
+
+
 class Attention(nn.Module):
-    """Grouped-query attention over INT4 q/k/v/o projections with RoPE and an append-only KV cache."""
+    """Grouped-query attention over INT4 q/k/v/o projections with RoPE and an in-place KV cache."""
 
     def __init__(self, q_proj, k_proj, v_proj, o_proj, heads, kv_heads, head_dim, rope_theta=1e6):
         super().__init__()
         self.q_proj, self.k_proj, self.v_proj, self.o_proj = q_proj, k_proj, v_proj, o_proj
         self.heads, self.kv_heads, self.head_dim, self.rope_theta = heads, kv_heads, head_dim, rope_theta
+        self.scale = head_dim ** -0.5
 
     def forward(self, values, cache=None):
         batch, steps, _ = values.shape
         q = self.q_proj(values).view(batch, steps, self.heads, self.head_dim).transpose(1, 2)
         k = self.k_proj(values).view(batch, steps, self.kv_heads, self.head_dim).transpose(1, 2)
         v = self.v_proj(values).view(batch, steps, self.kv_heads, self.head_dim).transpose(1, 2)
-        offset = 0 if cache is None or "k" not in cache else cache["k"].shape[2]
+        offset = 0 if cache is None else cache.length
         if steps > 1 and offset > 0:
             raise ValueError("multi-token continuation is not supported by this harness")
         positions = torch.arange(offset, offset + steps, device=values.device)
         q, k = _rope(q, positions, self.rope_theta), _rope(k, positions, self.rope_theta)
         if cache is not None:
-            if "k" in cache:
-                k = torch.cat([cache["k"], k], dim=2)
-                v = torch.cat([cache["v"], v], dim=2)
-            cache["k"], cache["v"] = k, v
-        out = nn.functional.scaled_dot_product_attention(q, k, v, is_causal=steps > 1 and offset == 0,
-                                                         enable_gqa=self.heads != self.kv_heads)
+            k, v = cache.update_and_fetch(k, v)
+        out = scaled_dot_product_attention(q, k, v, cache, self.scale, "causal" if steps > 1 else None)
         return self.o_proj(out.transpose(1, 2).reshape(batch, steps, self.heads * self.head_dim))
 
 
@@ -142,8 +184,13 @@ class TinyCausalLM(nn.Module):
         self.lm_head = lm_head
         self.vocab_size = vocab_size
 
-    def make_cache(self):
-        return [{} for _ in self.layers]
+    def make_cache(self, batch=1, capacity=64):
+        caches = []
+        for layer in self.layers:
+            attention = layer.self_attn
+            caches.append(KVCache(batch, attention.kv_heads, capacity, attention.head_dim,
+                                  attention.q_proj.weight.device))
+        return caches
 
     def forward(self, tokens, cache=None):
         hidden = self.embed_tokens(tokens)

@@ -7,6 +7,11 @@ torch-side equivalent of the reference's MLX-LM patcher (metile/integrations/mlx
     (:3791, :3927), admitted by structure (:186-237) and gated per call (:3805-3834)
   * fused decoder block: attention, fused add+RMSNorm, then down(swiglu(norm)) + hidden
     (:3689-3785, decision table in the same function)
+  * decode attention behind the model modules' `scaled_dot_product_attention` attribute
+    (:4607-4655), admitted per call by the reference's shape rule (:3558-3573); and, beyond the
+    reference, the whole decode step of an attention module as five kernels (fused q|k|v projection,
+    rotary embedding + in-place cache append, split-KV attention + merge, output projection with the
+    residual in its epilogue)
 
 What differs on purpose: there is no tournament and no silent rerouting to a "native wins"
 choice.  A call the kernels cannot serve (wrong format, dtype, device, an additive bias) runs the
@@ -16,6 +21,7 @@ module's ORIGINAL forward, and the reason is recorded once in `TorchPatch.refusa
 
 from __future__ import annotations
 
+import sys
 import weakref
 from dataclasses import dataclass, field
 
@@ -26,6 +32,7 @@ from .. import backends
 FEATURES = ("attention", "rms_norm", "graph_fusion", "quantized_mlp")
 _GATED_MLP_ATTRIBUTES = ("gate_proj", "up_proj", "down_proj")
 _FUSED_BLOCK_ATTRIBUTES = ("input_layernorm", "post_attention_layernorm", "mlp")
+_ATTENTION_ATTRIBUTES = ("q_proj", "k_proj", "v_proj", "o_proj")
 
 
 @dataclass
@@ -157,6 +164,75 @@ def execute_quantized_mlp(module, values, residual=None):
     return execute(values, residual)
 
 
+_qkv_cache = weakref.WeakKeyDictionary()
+
+
+def attention_decode_refusal(module, values, cache):
+    """None when the five-kernel decode step can serve this call of an attention module, else why not:
+    one new token per sequence, an in-place cache with room left, four affine 4-bit projections
+    without additive bias, bfloat16 activations on CUDA, and a head layout the kernels take."""
+    if values.ndim != 3 or values.shape[1] != 1:
+        return "not a single-token decode step"
+    if cache is None or not all(hasattr(cache, name) for name in ("keys", "values", "length", "positions", "advance")):
+        return "no in-place KV cache"
+    if cache.length < 1 or cache.length >= cache.keys.shape[2]:
+        return "the cache is empty or full"
+    for name in _ATTENTION_ATTRIBUTES:
+        linear = getattr(module, name, None)
+        if linear is None or not _is_affine_int4(linear):
+            return f"{name} is not an affine 4-bit group-64 quantized projection"
+        if getattr(linear, "bias", None) is not None:
+            return f"{name} has an additive bias"
+    heads, kv_heads, dim = (getattr(module, name, None) for name in ("heads", "kv_heads", "head_dim"))
+    if not heads or not kv_heads or dim not in (64, 128) or heads % kv_heads or heads // kv_heads > 8:
+        return "head layout outside what the decode kernel serves"
+    if getattr(module, "rope_theta", None) is None:
+        return "no rotary base"
+    if values.dtype != torch.bfloat16 or not values.is_cuda:
+        return "activations are not bfloat16 on a CUDA device"
+    if values.shape[0] != cache.keys.shape[0]:
+        return "batch does not match the cache"
+    return None
+
+
+def _fused_qkv(module):
+    """The q, k and v triples concatenated along the output axis, built once per module: one
+    projection launch reads the activations once and writes one q|k|v row per sequence."""
+    fused = _qkv_cache.get(module)
+    if fused is None:
+        parts = (module.q_proj, module.k_proj, module.v_proj)
+        fused = tuple(torch.cat([getattr(linear, name) for linear in parts], dim=0).contiguous()
+                      for name in ("weight", "scales", "biases"))
+        _qkv_cache[module] = fused
+    return fused
+
+
+def execute_attention_decode(module, values, cache, residual=None):
+    """One decode step of an attention module without a framework op between its kernels:
+    fused q|k|v projection, rotary embedding + cache append, attention over the cache, output
+    projection (+ residual, added to the un-rounded sum).  values [B, 1, H]; returns [B, 1, H]."""
+    batch = values.shape[0]
+    heads, kv_heads, dim = module.heads, module.kv_heads, module.head_dim
+    rows = values.reshape(batch, values.shape[-1])
+    qkv = backends.mlx_affine_qmv(rows, *_fused_qkv(module))
+    q = qkv[:, :heads * dim].view(batch, heads, dim)
+    k = qkv[:, heads * dim:(heads + kv_heads) * dim].view(batch, kv_heads, dim)
+    v = qkv[:, (heads + kv_heads) * dim:].view(batch, kv_heads, dim)
+    rotated = backends.rope_kv_append(q, k, v, cache.positions, cache.keys, cache.values, theta=module.rope_theta)
+    cache.advance(1)
+    scale = getattr(module, "scale", dim ** -0.5)
+    attended = backends.mlx_attention_decode(rotated.view(batch, heads, 1, dim), cache.keys[:, :, :cache.length],
+                                             cache.values[:, :, :cache.length], scale=scale)
+    attended = attended.view(batch, heads * dim)
+    o = module.o_proj
+    if residual is None:
+        out = backends.mlx_affine_qmv(attended, o.weight, o.scales, o.biases)
+    else:
+        out = backends.mlx_affine_residual_qmv(attended, o.weight, o.scales, o.biases,
+                                               residual.reshape(batch, residual.shape[-1]))
+    return out.view(values.shape)
+
+
 def _replace_forward(patch, cls, make_replacement):
     original = cls.forward
     if getattr(original, "_metile_original", None) is not None:
@@ -231,6 +307,53 @@ def _patch_rms_norm(model, patch):
         _replace_forward(patch, norm_class, make)
 
 
+def _patch_attention(model, patch):
+    """Decode attention.  Two surfaces, as far as the model offers them:
+    (1) the `scaled_dot_product_attention` attribute of the module that defines the model's attention
+        class is replaced by a function that serves single-row, unmasked calls with the decode kernel
+        and passes everything else to the original (the reference's scheme);
+    (2) attention classes with q/k/v/o projections and an in-place cache run their decode steps as five
+        kernels (execute_attention_decode); prefill and unsupported calls run the original forward."""
+    classes = [type(layer.self_attn) for layer in _model_layers(model) if getattr(layer, "self_attn", None) is not None]
+    before = len(patch.replacements)
+    for attention_class in dict.fromkeys(classes):
+        home = sys.modules.get(attention_class.__module__)
+        original_sdpa = getattr(home, "scaled_dot_product_attention", None)
+        if original_sdpa is not None and getattr(original_sdpa, "_metile_original", None) is None:
+
+            def metile_scaled_dot_product_attention(queries, keys, values, cache, scale, mask=None,
+                                                    _original=original_sdpa):
+                reason = backends.supports_attention_decode(queries, keys, values, mask)
+                if reason is None:
+                    return backends.mlx_attention_decode(queries, keys, values, scale=scale)
+                if queries.ndim == 4 and queries.shape[2] == 1:
+                    patch.refuse("attention", reason)
+                return _original(queries, keys, values, cache, scale, mask)
+
+            metile_scaled_dot_product_attention._metile_original = original_sdpa
+            patch.replacements.append((home, "scaled_dot_product_attention", original_sdpa))
+            home.scaled_dot_product_attention = metile_scaled_dot_product_attention
+
+        if not _structurally_matches(attention_class, _ATTENTION_ATTRIBUTES):
+            continue
+
+        def make(original):
+            def replacement(self, values, cache=None, *args, **kwargs):
+                if args or kwargs or values.ndim != 3 or values.shape[1] != 1:
+                    return original(self, values, cache, *args, **kwargs)  # prefill: the model's own path
+                reason = attention_decode_refusal(self, values, cache)
+                if reason is not None:
+                    patch.refuse("attention", reason)
+                    return original(self, values, cache)
+                return execute_attention_decode(self, values, cache)
+
+            return replacement
+
+        _replace_forward(patch, attention_class, make)
+    if len(patch.replacements) == before:
+        patch.refuse("attention", "the model exposes no attention surface that can be replaced")
+
+
 def _patch_graph_fusion(model, patch, quantized_mlp):
     classes = [type(layer) for layer in _model_layers(model)]
     for block_class in dict.fromkeys(classes):
@@ -248,8 +371,21 @@ def _patch_graph_fusion(model, patch, quantized_mlp):
                 if values.dtype != torch.bfloat16 or not values.is_cuda:
                     patch.refuse("graph_fusion", "activations are not bfloat16 on a CUDA device")
                     return original(self, values, *args, **kwargs)
-                attended = attention(self.input_layernorm(values), *args, **kwargs)
-                hidden, normalized = backends.mlx_add_rms_norm(values, attended, post.weight, eps)
+                normed_input = self.input_layernorm(values)
+                cache = args[0] if args else kwargs.get("cache")
+                fused_attention = (
+                    getattr(type(attention).forward, "_metile_original", None) is not None
+                    and len(args) <= 1 and set(kwargs) <= {"cache"}
+                    and _has_parts(attention, _ATTENTION_ATTRIBUTES)
+                    and attention_decode_refusal(attention, normed_input, cache) is None)
+                if fused_attention:
+                    # The residual rides in the output projection's epilogue (added to the un-rounded
+                    # sum), so only the norm is left of the add + RMSNorm.
+                    hidden = execute_attention_decode(attention, normed_input, cache, residual=values)
+                    normalized = backends.mlx_rms_norm(hidden, post.weight, eps)
+                else:
+                    attended = attention(normed_input, *args, **kwargs)
+                    hidden, normalized = backends.mlx_add_rms_norm(values, attended, post.weight, eps)
                 if quantized_mlp:
                     reason = quantized_mlp_refusal(self.mlp, normalized)
                     if reason is None:
@@ -266,7 +402,8 @@ def apply_metile_to_torch_lm(model=None, *, attention=False, rms_norm=True, grap
                              quantized_mlp=True, quantized_mlp_min_rows=1, quantized_mlp_max_rows=None):
     """Patch the classes `model`'s layers use and return the reversible handle.
 
-    attention: decode attention has no kernel in this package; asking for it is recorded as a refusal.
+    attention: single-row, unmasked attention calls run the decode-attention kernel; attention modules
+        with INT4 q/k/v/o projections and an in-place cache run a whole decode step as five kernels.
     rms_norm: RMSNorm modules run the CUDA RMSNorm.
     graph_fusion: decoder blocks run attention, then the fused residual add + RMSNorm, then (with
         quantized_mlp) the fused INT4 MLP with the residual folded into the down projection.
@@ -282,7 +419,7 @@ def apply_metile_to_torch_lm(model=None, *, attention=False, rms_norm=True, grap
         raise ValueError("quantized MLP maximum rows must not be smaller than its minimum")
     patch = TorchPatch()
     if attention:
-        patch.refuse("attention", "no decode-attention kernel in this package; the model's own attention runs")
+        _patch_attention(model, patch)
     if graph_fusion:
         _patch_graph_fusion(model, patch, quantized_mlp)
     if quantized_mlp:

@@ -51,6 +51,12 @@ def shard_down(triple, rank, world, group_size=64):
             biases[:, lo // group_size:hi // group_size].contiguous())
 
 
+def shard_mlp_weights(gate, up, down, rank, world, group_size=64):
+    """This rank's (gate, up, down) shards of full weight triples."""
+    return (shard_gate_up(gate, rank, world, group_size), shard_gate_up(up, rank, world, group_size),
+            shard_down(down, rank, world, group_size))
+
+
 class TensorParallelMLP:
     """down(swiglu(x)) + residual with the weights sharded over `world` ranks."""
 
@@ -61,18 +67,19 @@ class TensorParallelMLP:
         replaced to exercise the sharding logic without a GPU."""
         self.gate, self.up, self.down = gate, up, down
         self.rank, self.world, self.group = rank, world, group
-        if swiglu_fn is None:
-            from .backends.cuda_quantized import mlx_affine_swiglu as swiglu_fn
-        if down_fn is None:
-            from .backends.cuda_quantized import mlx_affine_qmv, mlx_affine_residual_qmv
-
-            def down_fn(hidden, weight, scales, biases, residual):
-                if residual is None:
-                    return mlx_affine_qmv(hidden, weight, scales, biases)
-                return mlx_affine_residual_qmv(hidden, weight, scales, biases, residual)
-
+        # With the CUDA operators, the shard's MLP is ONE C-ABI call on a bound executor (both kernels,
+        # workspace owned by the executor, the residual in rank 0's down epilogue): one Python dispatch
+        # and one all-reduce per MLP.  Injected stand-ins take the two-step path.
+        self._executor = None
         self._swiglu, self._down = swiglu_fn, down_fn
         self._all_reduce = all_reduce_fn or self._dist_all_reduce
+
+    def _bound_executor(self, values):
+        if self._executor is None:
+            from .backends.cuda_quantized import mlx_affine_mlp_executor
+
+            self._executor = mlx_affine_mlp_executor(values, *self.gate, *self.up, *self.down, None)
+        return self._executor
 
     def _dist_all_reduce(self, tensor):
         if self.world > 1:
@@ -104,7 +111,14 @@ class TensorParallelMLP:
         move = lambda triple: tuple(t.to(device) for t in triple)  # noqa: E731
         return cls(move(gate), move(up), move(down), rank, world, **kwargs)
 
-    def __call__(self, values, residual=None):
+    def partial(self, values, residual=None):
+        """This rank's partial output [M, H] (bf16): its K slice of the down projection, plus the
+        residual on rank 0."""
+        mine = residual if self.rank == 0 else None
+        if self._swiglu is None and self._down is None:
+            return self._bound_executor(values)(values, mine)
         hidden = self._swiglu(values, *self.gate, *self.up)
-        partial = self._down(hidden, *self.down, residual if self.rank == 0 else None)
-        return self._all_reduce(partial)
+        return self._down(hidden, *self.down, mine)
+
+    def __call__(self, values, residual=None):
+        return self._all_reduce(self.partial(values, residual))

@@ -315,3 +315,31 @@ def test_survivors_of_the_bisection_are_kept_together(fake_kernels):
         assert report.verified is True and report.difference == 0.0
     finally:
         report.restore()
+
+
+def test_attention_patch_replaces_the_module_level_primitive_and_restores_it():
+    """The attention feature swaps the `scaled_dot_product_attention` attribute of the module that
+    defines the model's attention class (as the reference swaps mlx_lm.models.base's) and the class's
+    forward; a call the kernel cannot serve (here: CPU tensors) is passed on and recorded."""
+    from metile_b200.integrations import blocks
+
+    model = blocks.random_model(seed=1, hidden=64, intermediate=128, heads=2, kv_heads=1, head_dim=64, layers=1,
+                                vocab=32, device="cpu")
+    original_sdpa, original_forward = blocks.scaled_dot_product_attention, blocks.Attention.forward
+    with torch_lm.apply_metile_to_torch_lm(model, attention=True, rms_norm=False, graph_fusion=False,
+                                           quantized_mlp=False) as patch:
+        assert blocks.scaled_dot_product_attention._metile_original is original_sdpa
+        assert blocks.Attention.forward._metile_original is original_forward
+        q = torch.randn((1, 2, 1, 64)).to(torch.bfloat16)
+        kv = torch.randn((1, 1, 5, 64)).to(torch.bfloat16)
+        out = blocks.scaled_dot_product_attention(q, kv, kv, None, 0.125, None)
+        assert out.shape == (1, 2, 1, 64)
+        assert "attention" in patch.refusals and "CUDA" in patch.refusals["attention"]
+        prefill = blocks.scaled_dot_product_attention(torch.randn((1, 2, 5, 64)).to(torch.bfloat16), kv, kv, None, 0.125,
+                                                      "causal")
+        assert prefill.shape == (1, 2, 5, 64)
+    assert blocks.scaled_dot_product_attention is original_sdpa and blocks.Attention.forward is original_forward
+    # A model without an attention surface says so instead of silently keeping the feature.
+    with torch_lm.apply_metile_to_torch_lm(FakeLM(), attention=True, rms_norm=False, graph_fusion=False,
+                                           quantized_mlp=False) as patch:
+        assert "no attention surface" in patch.refusals["attention"]

@@ -1,6 +1,6 @@
 """GPU tests at model level: `compile` on a seeded random-init decoder-only model with 4-bit
-projections, and one Qwen2.5-1.5B-shaped decoder block (BASELINE config 3: hidden 1536, 12 query /
-2 kv heads of 128, intermediate 8960, RoPE theta 1e6, eps 1e-6) in prefill and 16-row decode."""
+projections, and one Qwen2.5-1.5B-shaped decoder block (hidden 1536, 12 query / 2 kv heads of 128,
+intermediate 8960, RoPE theta 1e6, eps 1e-6) in prefill and 16-row decode."""
 
 import pytest
 import torch
@@ -25,7 +25,7 @@ def test_compile_verifies_a_random_model_and_reports(cuda_device):
         text = str(strict)
         assert "meTile on TinyCausalLM" in text
         for feature in strict.features:
-            assert feature in ("rms_norm", "graph_fusion", "quantized_mlp")
+            assert feature in ("attention", "rms_norm", "graph_fusion", "quantized_mlp")
         if "quantized_mlp" not in strict.features:
             assert "quantized_mlp" in strict.declined or "combined" in strict.declined
     finally:
@@ -34,8 +34,8 @@ def test_compile_verifies_a_random_model_and_reports(cuda_device):
     try:
         assert relaxed and relaxed.verified is True
         assert "quantized_mlp" in relaxed.features and "graph_fusion" in relaxed.features
-        assert "block" in relaxed.surfaces and "mlp" in relaxed.surfaces
-        assert "attention" in relaxed.declined
+        assert "block" in relaxed.surfaces and "mlp" in relaxed.surfaces and "self_attn" in relaxed.surfaces
+        assert "attention" in relaxed.features
         assert relaxed.relative is not None and relaxed.relative <= 2e-2
         with torch.no_grad():
             after = model(tokens).float()
@@ -49,11 +49,13 @@ def test_compile_verifies_a_random_model_and_reports(cuda_device):
 
 def test_patch_restores_every_class(cuda_device):
     model = blocks.random_model(seed=4, device=cuda_device, layers=1)
-    originals = (blocks.DecoderBlock.forward, blocks.GatedMLP.forward, blocks.RMSNorm.forward)
-    with torch_lm.apply_metile_to_torch_lm(model) as patch:
+    originals = (blocks.DecoderBlock.forward, blocks.GatedMLP.forward, blocks.RMSNorm.forward,
+                 blocks.Attention.forward, blocks.scaled_dot_product_attention)
+    with torch_lm.apply_metile_to_torch_lm(model, attention=True) as patch:
         assert blocks.DecoderBlock.forward._metile_original is originals[0]
-        assert len(patch.replacements) == 3
-    assert (blocks.DecoderBlock.forward, blocks.GatedMLP.forward, blocks.RMSNorm.forward) == originals
+        assert len(patch.replacements) == 5
+    assert (blocks.DecoderBlock.forward, blocks.GatedMLP.forward, blocks.RMSNorm.forward, blocks.Attention.forward,
+            blocks.scaled_dot_product_attention) == originals
 
 
 def qwen_block(device):
@@ -71,24 +73,36 @@ def qwen_block(device):
     return block, hidden
 
 
-def test_config3_qwen_block_prefill_and_decode(cuda_device):
-    """Patched vs unpatched block: prefill of 512 tokens, then a 16-row decode step at KV length 2048
-    (16 sequences, one new token each).  The patched block fuses add+RMSNorm and the INT4 MLP."""
+def block_cache(block, batch, length, capacity, device, seed):
+    attention = block.self_attn
+    cache = blocks.KVCache(batch, attention.kv_heads, capacity, attention.head_dim, device)
+    shape = (batch, attention.kv_heads, length, attention.head_dim)
+    cache.keys[:, :, :length] = synth.activations(seed, batch * attention.kv_heads * length, attention.head_dim,
+                                                  device, std=0.5).reshape(shape)
+    cache.values[:, :, :length] = synth.activations(seed + 1, batch * attention.kv_heads * length,
+                                                    attention.head_dim, device, std=0.5).reshape(shape)
+    cache.advance(length)
+    return cache
+
+
+def test_qwen_block_prefill_and_decode_patched_against_unpatched(cuda_device):
+    """One Qwen2.5-1.5B-shaped decoder block, patched vs unpatched: prefill of 512 tokens, then a 16-row
+    decode step at KV length 2048 (16 sequences, one new token each).  The patched decode step is
+    kernels only: RMSNorm, fused q|k|v, rotary + append, attention (+ merge), o-projection + residual,
+    RMSNorm, the INT4 MLP.  (The pieces are checked against the oracle in tests/test_gpu_configs.py.)"""
     block, hidden = qwen_block(cuda_device)
     model = torch.nn.Module()
     model.layers = torch.nn.ModuleList([block])
     prefill = synth.activations(1, 512, hidden, cuda_device, std=0.5).reshape(1, 512, hidden)
     decode = synth.activations(2, 16, hidden, cuda_device, std=0.5).reshape(16, 1, hidden)
-    kv = {"k": synth.activations(3, 16 * 2 * 2048, 128, cuda_device, std=0.5).reshape(16, 2, 2048, 128),
-          "v": synth.activations(4, 16 * 2 * 2048, 128, cuda_device, std=0.5).reshape(16, 2, 2048, 128)}
     with torch.no_grad():
-        ref_prefill = block(prefill, {})
-        ref_decode = block(decode, {k: v.clone() for k, v in kv.items()})
-        with torch_lm.apply_metile_to_torch_lm(model) as patch:
-            out_prefill = block(prefill, {})
-            out_decode = block(decode, {k: v.clone() for k, v in kv.items()})
+        ref_prefill = block(prefill, blocks.KVCache(1, 2, 512, 128, cuda_device))
+        ref_decode = block(decode, block_cache(block, 16, 2047, 2048, cuda_device, 3))
+        with torch_lm.apply_metile_to_torch_lm(model, attention=True) as patch:
+            out_prefill = block(prefill, blocks.KVCache(1, 2, 512, 128, cuda_device))
+            out_decode = block(decode, block_cache(block, 16, 2047, 2048, cuda_device, 3))
             assert not patch.refusals, patch.refusals
-            again = block(decode, {k: v.clone() for k, v in kv.items()})
+            again = block(decode, block_cache(block, 16, 2047, 2048, cuda_device, 3))
     for out, ref in ((out_prefill, ref_prefill), (out_decode, ref_decode)):
         assert out.shape == ref.shape and torch.isfinite(out.float()).all()
         peak = ref.float().abs().max()

@@ -26,12 +26,12 @@ from tests.helpers import assert_bit_equal, assert_within, f32, triple_np
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "kat.npz")
-FAMILIES = ("gemv", "umma", "umma_smem", "umma_scaled")
-MAX_ROWS = {"gemv": 8, "umma": 128, "umma_smem": 128, "umma_scaled": 16}
+FAMILIES = ("gemv", "umma")
+MAX_ROWS = {"gemv": 8, "umma": 128}
 
 
 def oracle_weights(family):
-    return "exact" if family in ("gemv", "umma_scaled") else "bf16"
+    return "exact" if family == "gemv" else "bf16"
 
 
 def bf16_tensor(bits, device):
@@ -141,7 +141,7 @@ SHAPES = [(64, 64), (256, 128), (512, 200), (1536, 1024), (2048, 512), (8192, 25
 @pytest.mark.parametrize("family", FAMILIES)
 @pytest.mark.parametrize("k,n", SHAPES)
 def test_projection_variants_against_oracle(cuda_device, family, k, n):
-    rows_list = {"gemv": (1, 2, 5, 8), "umma_scaled": (1, 3, 4, 7, 16)}.get(family, (1, 3, 16, 17, 64, 100, 128))
+    rows_list = {"gemv": (1, 2, 5, 8)}.get(family, (1, 3, 16, 17, 64, 100, 128))
     gate, up = synth.affine_weight(10, n, k, cuda_device), synth.affine_weight(11, n, k, cuda_device)
     gate_np, up_np = triple_np(gate), triple_np(up)
     weights = oracle_weights(family)
@@ -305,7 +305,7 @@ def test_batch_invariance_bit_exact_1_to_128(cuda_device, k, n):
         assert_bit_equal(B.mlx_affine_swiglu(x[shuffled], *gate, *up), alone_swi[shuffled], "shuffled batch")
 
 
-@pytest.mark.parametrize("family", ["gemv", "umma_smem", "umma_scaled"])
+@pytest.mark.parametrize("family", ["gemv", "umma"])
 def test_batch_invariance_within_each_family(cuda_device, family):
     k, n = 2048, 512
     gate, up = synth.affine_weight(10, n, k, cuda_device), synth.affine_weight(11, n, k, cuda_device)
@@ -313,7 +313,7 @@ def test_batch_invariance_within_each_family(cuda_device, family):
     x = synth.activations(99, top, k, cuda_device)
     with B.force_kernel(family):
         alone = torch.cat([B.mlx_affine_swiglu(x[i:i + 1], *gate, *up) for i in range(top)])
-        for rows in {"gemv": (2, 3, 4, 8), "umma_scaled": (2, 5, 16)}.get(family, (16, 33, 128)):
+        for rows in {"gemv": (2, 3, 4, 8)}.get(family, (16, 33, 128)):
             assert_bit_equal(B.mlx_affine_swiglu(x[:rows], *gate, *up), alone[:rows], f"{family} M={rows}")
 
 
