@@ -198,6 +198,29 @@ int mt_rope_kv_append(const void* q, const void* k, const void* v, long long row
                       const int* positions, void* q_out, void* k_cache, void* v_cache, int batch,
                       int q_heads, int kv_heads, int capacity, int head_dim, float theta, void* stream);
 
+/* Sum of bf16 partial results over the GPUs of one node (one process per GPU), for the
+ * tensor-parallel form of the fused MLP: the down projection of a K-sharded MLP leaves a partial
+ * [M, H] result on every rank.  NO COUNTERPART IN THE REFERENCE, which is single-device.
+ *
+ * One kernel per rank stores the partial into every peer's receive buffer over NVLink, signals, waits
+ * (bounded by limit_ms, 1..2000; on expiry nothing is written to `out` and mt_device_status reports
+ * code 0x9E0 with the peer that did not arrive) and adds the partials in rank order in fp32, so every
+ * rank obtains the same bits whatever the message size.
+ *
+ * mt_peer_group_create allocates this rank's receive buffer (the only allocation; `slot_bytes` =
+ * largest message in bytes, a multiple of 16, at most 64 MiB) and writes its 64-byte CUDA IPC handle to
+ * ipc_handle_out.  The caller exchanges the handles between the processes by any host means and passes
+ * all `world` of them, in rank order, to mt_peer_group_connect.  Every rank must call
+ * mt_peer_all_reduce the same number of times with the same `elements` (bf16 elements, a multiple
+ * of 8); `partial` and `out` may be the same buffer.  Before mt_peer_group_destroy the caller makes
+ * sure (a host barrier) that no peer has a call in flight. */
+int mt_peer_group_create(int rank, int world, size_t slot_bytes, void** group_out,
+                         void* ipc_handle_out);
+int mt_peer_group_connect(void* group, const void* ipc_handles);
+int mt_peer_all_reduce(void* group, const void* partial, void* out, size_t elements,
+                       unsigned int limit_ms, void* stream);
+int mt_peer_group_destroy(void* group);
+
 /* Dense bf16 small-batch projection, w [N, K] bf16: out = bf16(bf16(x @ w^T) + residual).
  * Every row is bit-identical to running it alone.  K % 128 == 0.  residual may be NULL.
  * Replaces: metile/compiler/dense.py:302 (lower_dense_residual_qmv) and its backend entry

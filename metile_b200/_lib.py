@@ -46,6 +46,10 @@ SIGNATURES = {
     "mt_attention_decode_workspace_bytes": (_z, [_i, _i, _i, _i]),
     "mt_attention_decode": (_i, [_p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _i, _i, _i, _f, _p]),
     "mt_rope_kv_append": (_i, [_p, _p, _p, ctypes.c_longlong, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]),
+    "mt_peer_group_create": (_i, [_i, _i, _z, ctypes.POINTER(ctypes.c_void_p), _p]),
+    "mt_peer_group_connect": (_i, [_p, _p]),
+    "mt_peer_all_reduce": (_i, [_p, _p, _p, _z, _u, _p]),
+    "mt_peer_group_destroy": (_i, [_p]),
     "mt_dense_rows": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
     "mt_dense_swiglu": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
     "mt_dense_act": (_i, [_p, _p, _p, _i, _i, _i, _u, _p]),

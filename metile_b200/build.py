@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUTPUT = os.path.join(CSRC, "libmetile_b200.so")
 SOURCES = ("metile_b200.cu",)
-HEADERS = ("common.cuh", "ptx.cuh", "affine_gemv.cuh", "affine_umma.cuh", "affine_mlp_fused.cuh", "add_rmsnorm.cuh", "attention_decode.cuh",
+HEADERS = ("common.cuh", "ptx.cuh", "affine_gemv.cuh", "affine_umma.cuh", "affine_mlp_fused.cuh", "add_rmsnorm.cuh", "attention_decode.cuh", "peer_reduce.cuh",
            "dense_rows.cuh", os.path.join("..", "..", "include", "metile_b200.h"))
 
 

@@ -136,20 +136,6 @@ __host__ __device__ inline FusedMlpLayout fused_mlp_layout(int M, int H, int I, 
     return l;
 }
 
-// The eight nibbles of a word as the floats 128+e0 .. 128+e7 (natural order).
-__device__ __forceinline__ void unpack_word_f32_offset128(uint32_t w, float (&q)[8]) {
-    const uint32_t even = w & 0x0F0F0F0Fu, odd = (w >> 4) & 0x0F0F0F0Fu;
-    constexpr uint32_t kMagic = 0x43000000u;  // 128.0f
-    q[0] = __uint_as_float(__byte_perm(even, kMagic, 0x7044));
-    q[1] = __uint_as_float(__byte_perm(odd, kMagic, 0x7044));
-    q[2] = __uint_as_float(__byte_perm(even, kMagic, 0x7144));
-    q[3] = __uint_as_float(__byte_perm(odd, kMagic, 0x7144));
-    q[4] = __uint_as_float(__byte_perm(even, kMagic, 0x7244));
-    q[5] = __uint_as_float(__byte_perm(odd, kMagic, 0x7244));
-    q[6] = __uint_as_float(__byte_perm(even, kMagic, 0x7344));
-    q[7] = __uint_as_float(__byte_perm(odd, kMagic, 0x7344));
-}
-
 // Barrier among the compute warps only (the producer warp keeps feeding the ring).
 __device__ __forceinline__ void fused_compute_sync() {
     asm volatile("bar.sync 1, %0;" ::"r"(kFusedComputeThreads) : "memory");

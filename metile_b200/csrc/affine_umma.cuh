@@ -27,7 +27,8 @@
 //                    zero-filled) arrives by TMA straight into the swizzled B tile: no thread touches
 //                    the activations, whose handling cost as many instructions as the dequantisation
 //                    at 128 rows when every dequant thread did a share of it
-//   MMA lane       : tcgen05.mma kind::f16 (bf16 x bf16 -> fp32 in TMEM), tcgen05.commit
+//   MMA lanes      : two threads issue tcgen05.mma kind::f16 (bf16 x bf16 -> fp32 in TMEM) and
+//                    tcgen05.commit, one per tile (gate / up) or per k-block parity (single tile)
 //   epilogue       : tcgen05.ld -> fp32 partial tile in shared memory; when the K range is split
 //                    over a thread-block cluster the partials are summed over DSMEM in rank order;
 //                    then SwiGLU / residual, bf16 store (coalesced along N)
@@ -68,16 +69,24 @@ struct UmmaConfig {
     static constexpr int kProducerWarp = kDequantWarps;
     static constexpr int kMmaWarp = kDequantWarps + 1;
     static constexpr int kXWarp = kDequantWarps + 2;
-    static constexpr int kThreads = (kDequantWarps + 3) * 32;
+    static constexpr int kMmaWarp2 = kDequantWarps + 3;
+    static constexpr int kThreads = (kDequantWarps + 4) * 32;
     static constexpr int kWTileBytes = kUmmaTileRows * 128;         // one packed tile, four k-blocks
     static constexpr int kSlotBytes = kT * kWTileBytes;
     static constexpr int kBBytes = kMPad * 128;                     // activation tile of one k-block
     static constexpr int kAbBytes = kBBytes;                        // operand bytes per stage in shared memory (A lives in tensor memory)
+    // Four operand stages.  A ring of activation tiles of its own, eight k-blocks ahead of the A
+    // stages, was measured and was slower (617 against 559 cycles per k-block at 16 rows): the extra
+    // wait and commit per k-block in the issuing threads cost more than the earlier request saved.
     static constexpr int kAbStages = 4;
-    // One accumulator per tile.  Measured on B200: a tcgen05.mma with M=128, K=16 costs ~45 cycles
-    // for any N <= 64 (64 for N=128, 128 for N=256) whether or not consecutive instructions share an
-    // accumulator, so splitting the K steps over several accumulators buys nothing.
-    static constexpr int kAcc = 1;
+    // Two threads (in two warps) issue the MMAs.  One issuer's loop per k-block -- poll the operand
+    // barrier (~140 cycles even when it is already complete), four MMAs whose issue blocks while the
+    // pipe is busy, commit -- measured 566 cycles per k-block at 16 rows, more than twice what the
+    // tensor pipe needs for the four MMAs (45-67 cycles each), so the issuers alternate.  With two
+    // tiles per CTA each issuer owns one tile (gate / up) and its accumulator; with one tile the
+    // issuers take the even and the odd k-blocks and accumulate into two accumulators that the
+    // epilogue adds (even + odd), an order that depends on K only.
+    static constexpr int kAcc = kT == 1 ? 2 : 1;
     static constexpr int kAccCols = kT * kAcc * kMPad;
     static constexpr int kATmemCols = kAbStages * kT * 32;
     static constexpr int kTmemCols = pow2_at_least(kAccCols + kATmemCols);
@@ -165,6 +174,45 @@ __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
     return v;
 }
 
+// The loop of one of the two MMA-issuing threads.  kIssuer picks the tile (two tiles per CTA) or the
+// parity of the k-blocks (one tile).  The thread's loop is kept to a few instructions per MMA: the
+// operand descriptor of byte 0 of the operand area is built once and every other descriptor is that
+// value plus a compile-time offset (the start-address field counts 16-byte units and never carries
+// out of its 14 bits), and the loop over k-blocks is unrolled by the number of operand stages so that
+// stage indices are constants.
+template <int kT, int kMPad, int kIssuer>
+__device__ __forceinline__ void umma_issue(uint32_t tmem_base, const uint8_t* ab, uint64_t* ab_full, uint64_t* ab_empty,
+                                           uint64_t* acc_full, volatile int* abort_flag, int nkb) {
+    using Cfg = UmmaConfig<kT, kMPad>;
+    constexpr uint32_t idesc = ptx::umma_idesc_bf16(kUmmaTileRows, kMPad);
+    constexpr int t = kT == 2 ? kIssuer : 0;          // the tile this thread accumulates
+    constexpr int chain = kT == 2 ? 0 : kIssuer;      // its accumulator within the tile
+    const uint32_t d_tmem = tmem_base + (t * Cfg::kAcc + chain) * kMPad;
+    const uint64_t desc0 = ptx::smem_desc_k_major_sw128(ptx::smem_u32(ab));
+    for (int i0 = 0; i0 < nkb; i0 += Cfg::kAbStages) {
+        const uint32_t phase = (i0 / Cfg::kAbStages) & 1;
+        const uint32_t later = i0 > 0 ? 1u : 0u;
+#pragma unroll
+        for (int a = 0; a < Cfg::kAbStages; ++a) {
+            if (kT == 1 && (a & 1) != kIssuer) continue;
+            const int i = i0 + a;
+            if (i >= nkb) break;
+            if (!ptx::mbar_wait_spin(&ab_full[a], phase, abort_flag, kWaitAbFull)) { i0 = nkb; break; }
+            ptx::tc_fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < kUmmaBlockK / 16; ++ks) {
+                const uint64_t b_desc = desc0 + (uint64_t)((a * Cfg::kAbBytes + ks * 32) >> 4);
+                // The first MMA into an accumulator overwrites it.
+                const uint32_t accumulate = (ks > 0 || a > (kT == 1 ? kIssuer : 0)) ? 1u : later;
+                const uint32_t a_tmem = tmem_base + Cfg::kAccCols + (a * kT + t) * 32 + ks * 8;
+                ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+            }
+            ptx::umma_commit(&ab_empty[a]);
+        }
+    }
+    ptx::umma_commit(acc_full);
+}
+
 template <int kT, int kMPad, bool kSwiglu>
 __global__ void __launch_bounds__(UmmaConfig<kT, kMPad>::kThreads, UmmaConfig<kT, kMPad>::kAllowedPerSm)
 affine_umma_kernel(const __grid_constant__ UmmaParams p) {
@@ -206,9 +254,9 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
         }
         for (int i = 0; i < Cfg::kAbStages; ++i) {
             ptx::mbar_init(&ab_full[i], Cfg::kWarpsPerKBlock + 1);  // dequant warps + the activation tile's copy
-            ptx::mbar_init(&ab_empty[i], 1);
+            ptx::mbar_init(&ab_empty[i], kT == 2 ? 2 : 1);  // two tiles: both issuers read the stage
         }
-        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_full, 2);
         *abort_flag = 0;
         ptx::mbar_fence_init();
     }
@@ -273,42 +321,10 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
             }
         }
     } else if (warp == Cfg::kMmaWarp) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::umma_idesc_bf16(kUmmaTileRows, kMPad);
-            // This one thread issues every MMA, so its loop is kept to a few instructions per MMA:
-            // the operand descriptor of byte 0 of the operand area is built once and every other
-            // descriptor is that value plus a compile-time offset (the start-address field counts
-            // 16-byte units and never carries out of its 14 bits), and the loop over k-blocks is
-            // unrolled by the number of operand stages so that stage indices are constants.
-            const uint64_t desc0 = ptx::smem_desc_k_major_sw128(ptx::smem_u32(ab));
-            for (int i0 = 0; i0 < nkb; i0 += Cfg::kAbStages) {
-                const uint32_t phase = (i0 / Cfg::kAbStages) & 1;
-                const uint32_t later = i0 > 0 ? 1u : 0u;
-#pragma unroll
-                for (int a = 0; a < Cfg::kAbStages; ++a) {
-                    const int i = i0 + a;
-                    if (i >= nkb) break;
-                    if (!ptx::mbar_wait(&ab_full[a], phase, abort_flag, kWaitAbFull)) { i0 = nkb; break; }
-                    ptx::tc_fence_after_sync();
-#pragma unroll
-                    for (int ks = 0; ks < kUmmaBlockK / 16; ++ks) {
-#pragma unroll
-                        for (int t = 0; t < kT; ++t) {
-                            const int chain = ks % Cfg::kAcc;
-                            const uint32_t d_tmem = tmem_base + (t * Cfg::kAcc + chain) * kMPad;
-                            const uint64_t b_desc =
-                                desc0 + (uint64_t)((a * Cfg::kAbBytes + ks * 32) >> 4);
-                            const uint32_t accumulate = (a > 0 || ks >= Cfg::kAcc) ? 1u : later;
-                            const uint32_t a_tmem = tmem_base + Cfg::kAccCols + (a * kT + t) * 32 + ks * 8;
-                            ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
-                        }
-                    }
-                    ptx::umma_commit(&ab_empty[a]);
-                }
-            }
-            ptx::umma_commit(acc_full);
-        }
+        // ------------------------------------------------------------------ MMA issuers
+        if (lane == 0) umma_issue<kT, kMPad, 0>(tmem_base, ab, ab_full, ab_empty, acc_full, abort_flag, nkb);
+    } else if (warp == Cfg::kMmaWarp2) {
+        if (lane == 0) umma_issue<kT, kMPad, 1>(tmem_base, ab, ab_full, ab_empty, acc_full, abort_flag, nkb);
     } else {
         // ------------------------------------------------------------------ dequant warps
         const int group = warp >> 2;                   // four warps = one group = 128 rows
@@ -400,6 +416,7 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 if (ok) {
 #pragma unroll
                     for (int chain = 0; chain < Cfg::kAcc; ++chain) {
+                        if (chain > 0 && nkb < 2) break;  // the odd k-blocks' accumulator was never written
                         uint32_t part[16];
                         ptx::tmem_ld16(tmem_base + ((uint32_t)((warp & 3) << 5) << 16) +
                                            (t * Cfg::kAcc + chain) * kMPad + c0, part);

@@ -52,6 +52,20 @@ __device__ __forceinline__ void unpack_word_offset128(uint32_t w, uint32_t* out)
         asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(out[i]) : "r"(w >> (4 * i)), "r"(0x000F000Fu), "r"(0x43004300u));
 }
 
+// The eight nibbles of a word as the floats 128+e0 .. 128+e7 (natural order).
+__device__ __forceinline__ void unpack_word_f32_offset128(uint32_t w, float (&q)[8]) {
+    const uint32_t even = w & 0x0F0F0F0Fu, odd = (w >> 4) & 0x0F0F0F0Fu;
+    constexpr uint32_t kMagic = 0x43000000u;  // 128.0f
+    q[0] = __uint_as_float(__byte_perm(even, kMagic, 0x7044));
+    q[1] = __uint_as_float(__byte_perm(odd, kMagic, 0x7044));
+    q[2] = __uint_as_float(__byte_perm(even, kMagic, 0x7144));
+    q[3] = __uint_as_float(__byte_perm(odd, kMagic, 0x7144));
+    q[4] = __uint_as_float(__byte_perm(even, kMagic, 0x7244));
+    q[5] = __uint_as_float(__byte_perm(odd, kMagic, 0x7244));
+    q[6] = __uint_as_float(__byte_perm(even, kMagic, 0x7344));
+    q[7] = __uint_as_float(__byte_perm(odd, kMagic, 0x7344));
+}
+
 __device__ __forceinline__ float warp_sum_xor(float v) {
 #pragma unroll
     for (int offset = 16; offset >= 1; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);

@@ -9,7 +9,7 @@
 //   residual : bf16(bf16(acc) + residual)
 //   SwiGLU   : l = bf16(gate), r = bf16(up), y = 1/(1+exp(|l|)), sig = bf16(l<0 ? y : 1-y),
 //              out = bf16(bf16(l*sig) * r)
-// One warp produces kOut outputs for all kM rows.  HBM-bound: the weight matrix is read once.
+// One warp produces kOut outputs for all rows of a pass; up to 32 rows share one pass over the matrix.
 #pragma once
 
 #include "common.cuh"
@@ -26,10 +26,13 @@ __device__ __forceinline__ float round_bf16(float v) { return bf16_bits_to_f32(f
 
 enum class DenseEpilogue { kPlain, kSwiglu };
 
-template <int kM, int kOut, DenseEpilogue kEp>
+// kM: activation rows of the launch's template (rows past `rows` are computed on row `rows - 1`'s
+// activations and not stored); kOut: outputs per warp; kAhead: 128-column blocks whose weights are
+// requested together (bytes in flight per lane = kAhead * kOut * kStreams * 8).
+template <int kM, int kOut, int kAhead, DenseEpilogue kEp>
 __global__ void __launch_bounds__(256)
 dense_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w0, const uint16_t* __restrict__ w1,
-                  const uint16_t* __restrict__ residual, uint16_t* __restrict__ out, int K, int N) {
+                  const uint16_t* __restrict__ residual, uint16_t* __restrict__ out, int rows, int K, int N) {
     constexpr int kStreams = kEp == DenseEpilogue::kSwiglu ? 2 : 1;
     const int lane = threadIdx.x & 31;
     const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -48,33 +51,44 @@ dense_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w
 #pragma unroll
         for (int o = 0; o < kOut; ++o) row_offset[o] = (size_t)min(out_base + o, N - 1) * K;
 
-#pragma unroll 2
-        for (int b = 0; b < blocks; ++b) {
-            const int k = (b << 7) + (lane << 2);
-            uint2 wv[kStreams][kOut];
+        for (int b0 = 0; b0 < blocks; b0 += kAhead) {
+            // Request the weights of kAhead blocks before any of them is used: the kernel streams the
+            // matrix once, so what matters is how many bytes each warp keeps in flight.
+            uint2 wv[kAhead][kStreams][kOut];
 #pragma unroll
-            for (int s = 0; s < kStreams; ++s)
+            for (int a = 0; a < kAhead; ++a) {
+                const int k = (min(b0 + a, blocks - 1) << 7) + (lane << 2);
 #pragma unroll
-                for (int o = 0; o < kOut; ++o)
-                    wv[s][o] = ldg_stream_u2(reinterpret_cast<const uint2*>((s == 0 ? w0 : w1) + row_offset[o] + k));
-            float xf[kM][4];
+                for (int s = 0; s < kStreams; ++s)
 #pragma unroll
-            for (int m = 0; m < kM; ++m) {
-                const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)m * K + k));
-                xf[m][0] = bf16_lo(xv.x); xf[m][1] = bf16_hi(xv.x);
-                xf[m][2] = bf16_lo(xv.y); xf[m][3] = bf16_hi(xv.y);
+                    for (int o = 0; o < kOut; ++o)
+                        wv[a][s][o] = ldg_stream_u2(reinterpret_cast<const uint2*>((s == 0 ? w0 : w1) + row_offset[o] + k));
             }
 #pragma unroll
-            for (int s = 0; s < kStreams; ++s)
+            for (int a = 0; a < kAhead; ++a) {
+                if (b0 + a >= blocks) break;  // ascending block order, whatever kAhead is
+                const int k = ((b0 + a) << 7) + (lane << 2);
+                float wf[kStreams][kOut][4];
 #pragma unroll
-                for (int o = 0; o < kOut; ++o) {
-                    const float wf[4] = {bf16_lo(wv[s][o].x), bf16_hi(wv[s][o].x), bf16_lo(wv[s][o].y),
-                                         bf16_hi(wv[s][o].y)};
+                for (int s = 0; s < kStreams; ++s)
 #pragma unroll
-                    for (int m = 0; m < kM; ++m)
+                    for (int o = 0; o < kOut; ++o) {
+                        wf[s][o][0] = bf16_lo(wv[a][s][o].x); wf[s][o][1] = bf16_hi(wv[a][s][o].x);
+                        wf[s][o][2] = bf16_lo(wv[a][s][o].y); wf[s][o][3] = bf16_hi(wv[a][s][o].y);
+                    }
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) acc[s][o][m] = fmaf(wf[c], xf[m][c], acc[s][o][m]);
+                for (int m = 0; m < kM; ++m) {
+                    const int row = kM <= 8 ? m : min(m, rows - 1);
+                    const uint2 xv = __ldg(reinterpret_cast<const uint2*>(x + (size_t)row * K + k));
+                    const float xf[4] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y)};
+#pragma unroll
+                    for (int s = 0; s < kStreams; ++s)
+#pragma unroll
+                        for (int o = 0; o < kOut; ++o)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) acc[s][o][m] = fmaf(wf[s][o][c], xf[c], acc[s][o][m]);
                 }
+            }
         }
 
 #pragma unroll
@@ -96,6 +110,7 @@ dense_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w
                 if (n >= N) continue;
 #pragma unroll
                 for (int m = 0; m < kM; ++m) {
+                    if (m >= rows) break;
                     float v;
                     if constexpr (kEp == DenseEpilogue::kSwiglu) {
                         const float left = round_bf16(acc[0][o][m]);
@@ -116,14 +131,17 @@ dense_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w
 
 template <int kM, DenseEpilogue kEp>
 inline int launch_dense_m(const uint16_t* x, const uint16_t* w0, const uint16_t* w1, const uint16_t* residual,
-                          uint16_t* out, int K, int N, int sm_count, cudaStream_t stream) {
+                          uint16_t* out, int rows, int K, int N, int sm_count, cudaStream_t stream) {
     constexpr int kStreams = kEp == DenseEpilogue::kSwiglu ? 2 : 1;
-    constexpr int kOut = (kM * kStreams <= 2) ? 4 : (kM * kStreams <= 8 ? 2 : 1);
+    // One output per warp and many warps: the fp32 order of an output is fixed (one warp, ascending
+    // blocks), so parallelism comes from the outputs.  Few rows: six blocks of weights in flight per warp.
+    constexpr int kOut = (kM * kStreams <= 4) ? 2 : 1;
+    constexpr int kAhead = kM * kStreams <= 8 ? (kOut == 2 ? 3 : 6) : 3;
     const int warps_needed = (N + kOut - 1) / kOut;
     int grid = (warps_needed + 7) / 8;
     const int cap = sm_count * 8;
     if (grid > cap) grid = cap;
-    dense_rows_kernel<kM, kOut, kEp><<<grid, 256, 0, stream>>>(x, w0, w1, residual, out, K, N);
+    dense_rows_kernel<kM, kOut, kAhead, kEp><<<grid, 256, 0, stream>>>(x, w0, w1, residual, out, rows, K, N);
     return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
 }
 
@@ -137,23 +155,29 @@ inline int launch_dense(const void* x, const void* w0, const void* w1, const voi
     const uint16_t* bp = static_cast<const uint16_t*>(w1);
     const uint16_t* rp = static_cast<const uint16_t*>(residual);
     uint16_t* op = static_cast<uint16_t*>(out);
-    // Batches above 8 rows run as chunks of up to 8; each chunk re-reads the weights (from L2 for
-    // matrices that fit there).  The per-row result is the same in any chunking.
-    for (int m0 = 0; m0 < M; m0 += 8) {
-        const int rows = M - m0 < 8 ? M - m0 : 8;
+    // Up to 32 rows share one pass over the weights (the reference's kernels stop at 31); larger
+    // batches run as chunks of 32, whose re-reads of the matrix come from L2 when it fits there.
+    // A row's result is the same in any chunking: its fp32 order depends on (K, lane) only.
+    constexpr int kChunk = kEp == DenseEpilogue::kSwiglu ? 16 : 32;
+    for (int m0 = 0; m0 < M; m0 += kChunk) {
+        const int rows = M - m0 < kChunk ? M - m0 : kChunk;
         const uint16_t* xc = xp + (size_t)m0 * K;
         const uint16_t* rc = rp ? rp + (size_t)m0 * N : nullptr;
         uint16_t* oc = op + (size_t)m0 * N;
         int rc_code;
         switch (rows) {
-            case 1: rc_code = launch_dense_m<1, kEp>(xc, ap, bp, rc, oc, K, N, sm_count, stream); break;
-            case 2: rc_code = launch_dense_m<2, kEp>(xc, ap, bp, rc, oc, K, N, sm_count, stream); break;
-            case 3: rc_code = launch_dense_m<3, kEp>(xc, ap, bp, rc, oc, K, N, sm_count, stream); break;
-            case 4: rc_code = launch_dense_m<4, kEp>(xc, ap, bp, rc, oc, K, N, sm_count, stream); break;
-            case 5: rc_code = launch_dense_m<5, kEp>(xc, ap, bp, rc, oc, K, N, sm_count, stream); break;
-            case 6: rc_code = launch_dense_m<6, kEp>(xc, ap, bp, rc, oc, K, N, sm_count, stream); break;
-            case 7: rc_code = launch_dense_m<7, kEp>(xc, ap, bp, rc, oc, K, N, sm_count, stream); break;
-            default: rc_code = launch_dense_m<8, kEp>(xc, ap, bp, rc, oc, K, N, sm_count, stream); break;
+            case 1: rc_code = launch_dense_m<1, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
+            case 2: rc_code = launch_dense_m<2, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
+            case 3: rc_code = launch_dense_m<3, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
+            case 4: rc_code = launch_dense_m<4, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
+            case 5: rc_code = launch_dense_m<5, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
+            case 6: rc_code = launch_dense_m<6, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
+            case 7: rc_code = launch_dense_m<7, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
+            case 8: rc_code = launch_dense_m<8, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
+            default:
+                if (rows <= 16 || kChunk == 16) rc_code = launch_dense_m<16, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream);
+                else rc_code = launch_dense_m<kChunk, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream);
+                break;
         }
         if (rc_code != MT_OK) return rc_code;
     }

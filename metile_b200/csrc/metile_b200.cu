@@ -4,9 +4,12 @@
 
 #include "add_rmsnorm.cuh"
 #include "attention_decode.cuh"
+#include "peer_reduce.cuh"
 #include "affine_gemv.cuh"
 #include "affine_umma.cuh"
 #include "affine_mlp_fused.cuh"
+#include <string.h>
+
 #include "common.cuh"
 #include "dense_rows.cuh"
 
@@ -524,6 +527,83 @@ int mt_dense_act(const void* a, const void* b, void* c, int M, int N, int K, uns
         static_cast<const uint16_t*>(a), static_cast<const uint16_t*>(b), static_cast<uint16_t*>(c), M, N, K,
         (flags & MT_FLAG_GELU) ? 1 : 0);
     return cudaGetLastError() == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
+}
+
+// ---- tensor-parallel sum over the GPUs of one node (peer stores over NVLink) --------------------------
+
+int mt_peer_group_create(int rank, int world, size_t slot_bytes, void** group_out, void* ipc_handle_out) {
+    if (!group_out || !ipc_handle_out) return MT_ERR_NULL;
+    if (world < 1 || world > kPeerMaxWorld || rank < 0 || rank >= world) return MT_ERR_SHAPE;
+    if (slot_bytes == 0 || slot_bytes % 16 || slot_bytes > (64u << 20)) return MT_ERR_SHAPE;
+    if (!device_is_sm100()) return MT_ERR_DEVICE;
+    PeerGroup* group = new PeerGroup();
+    group->rank = rank;
+    group->world = world;
+    group->slot_bytes = slot_bytes;
+    group->flags_offset = 2 * (size_t)world * slot_bytes;
+    void* memory = nullptr;
+    const size_t bytes = peer_group_bytes(world, slot_bytes);
+    if (cudaGetDevice(&group->device) != cudaSuccess || cudaMalloc(&memory, bytes) != cudaSuccess) {
+        delete group;
+        return MT_ERR_LAUNCH;
+    }
+    cudaIpcMemHandle_t handle;
+    if (cudaMemset(memory, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+        cudaIpcGetMemHandle(&handle, memory) != cudaSuccess) {
+        cudaFree(memory);
+        delete group;
+        return MT_ERR_LAUNCH;
+    }
+    group->peers[rank] = static_cast<unsigned char*>(memory);
+    static_assert(sizeof(handle) == 64, "CUDA IPC handles are 64 bytes");
+    memcpy(ipc_handle_out, &handle, sizeof(handle));
+    *group_out = group;
+    return MT_OK;
+}
+
+int mt_peer_group_connect(void* group_pointer, const void* ipc_handles) {
+    if (!group_pointer || !ipc_handles) return MT_ERR_NULL;
+    PeerGroup* group = static_cast<PeerGroup*>(group_pointer);
+    if (group->connected) return MT_OK;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device != group->device) return MT_ERR_DEVICE;
+    for (int peer = 0; peer < group->world; ++peer) {
+        if (peer == group->rank) continue;
+        cudaIpcMemHandle_t handle;
+        memcpy(&handle, static_cast<const unsigned char*>(ipc_handles) + 64 * (size_t)peer, sizeof(handle));
+        void* mapped = nullptr;
+        if (cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            return MT_ERR_LAUNCH;
+        }
+        group->peers[peer] = static_cast<unsigned char*>(mapped);
+        group->opened[peer] = true;
+    }
+    group->connected = true;
+    return MT_OK;
+}
+
+int mt_peer_all_reduce(void* group_pointer, const void* partial, void* out, size_t elements, unsigned int limit_ms,
+                       void* stream) {
+    if (!group_pointer || !partial || !out) return MT_ERR_NULL;
+    PeerGroup* group = static_cast<PeerGroup*>(group_pointer);
+    if (!group->connected && group->world > 1) return MT_ERR_WORKSPACE;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device != group->device) return MT_ERR_DEVICE;
+    if (limit_ms < 1 || limit_ms > 2000) return MT_ERR_SHAPE;
+    return launch_peer_reduce(group, partial, out, elements, 1000000ull * limit_ms, static_cast<cudaStream_t>(stream));
+}
+
+int mt_peer_group_destroy(void* group_pointer) {
+    if (!group_pointer) return MT_OK;
+    PeerGroup* group = static_cast<PeerGroup*>(group_pointer);
+    int rc = MT_OK;
+    if (cudaDeviceSynchronize() != cudaSuccess) rc = MT_ERR_LAUNCH;
+    for (int peer = 0; peer < group->world; ++peer)
+        if (group->opened[peer] && cudaIpcCloseMemHandle(group->peers[peer]) != cudaSuccess) rc = MT_ERR_LAUNCH;
+    if (group->peers[group->rank] && cudaFree(group->peers[group->rank]) != cudaSuccess) rc = MT_ERR_LAUNCH;
+    delete group;
+    return rc;
 }
 
 }  // extern "C"

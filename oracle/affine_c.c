@@ -40,6 +40,15 @@ static inline uint16_t f32_to_bf16(float v) {
     return (uint16_t)(bits >> 16);
 }
 
+/* Sets the OpenMP thread count (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void oracle_set_threads(int threads) {
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -35,6 +35,12 @@ def num_threads():
     return int(lib().oracle_num_threads())
 
 
+def set_threads(threads):
+    """Use `threads` OpenMP threads from now on (a launcher may have exported OMP_NUM_THREADS=1)."""
+    lib().oracle_set_threads(int(threads))
+    return num_threads()
+
+
 def qmm(x_bits, packed, scale_bits, bias_bits, residual_bits=None):
     x = _u16(x_bits)
     m, k = x.shape
