@@ -916,6 +916,19 @@ def run_capture(spec):
     family = None if family == "default" else family
     hidden, inter = 2048, 8192
     device = torch.device("cuda:0")
+    if op == "attention":
+        # `rows` sequences x 2 KV heads x 2048 tokens x 128: six caches of 4 MB per sequence rotate.
+        heads, kv_heads, tokens, dim = 12, 2, 2048, 128
+        query = synth.activations(1, rows * heads, dim, device).reshape(rows, heads, 1, dim)
+        caches = [(synth.activations(10 + i, rows * kv_heads * tokens, dim, device, std=0.5).reshape(rows, kv_heads, tokens, dim),
+                   synth.activations(20 + i, rows * kv_heads * tokens, dim, device, std=0.5).reshape(rows, kv_heads, tokens, dim))
+                  for i in range(6)]
+        for keys, values in caches:
+            B.mlx_attention_decode(query, keys, values, scale=dim ** -0.5)
+        torch.cuda.synchronize()
+        ok, words = _lib.device_status()
+        print(json.dumps({"capture": spec, "device_status_ok": bool(ok)}))
+        return 0 if ok else 1
     sets = [synth.mlp_weights(200 + i, hidden, inter, device) for i in range(6)]
     x = synth.activations(5, rows, hidden, device)
     h = synth.activations(6, rows, inter, device, std=0.3)
@@ -949,7 +962,8 @@ def main():
     parser.add_argument("--skip-other", action="store_true", help="leave out the other named workloads")
     parser.add_argument("--capture", default=None, metavar="OP:FAMILY:ROWS",
                         help="run a few launches of one operator and exit (a small target for ncu): OP is mlp, "
-                             "swiglu or down; FAMILY is default, mlp_fused, mlp_fused_mma, gemv or umma")
+                             "swiglu, down or attention (ROWS = sequences); FAMILY is default, mlp_fused, "
+                             "mlp_fused_mma, gemv or umma")
     args = parser.parse_args()
     if args.capture:
         return run_capture(args.capture)

@@ -10,9 +10,12 @@
 // every query head of a KV head, so each cache byte is read once.
 //
 // Split over the KV range ("flash decoding"): CTA (s, b*Hkv + h) takes tokens [128 s, 128 s + 128) of
-// one (sequence, KV head); warp w takes 32 of them, one token per lane.
-//   scores : the lane reads ITS token's key row (16 bytes per load) and multiplies it with the G
-//            scaled query rows, which sit in shared memory as fp32 (broadcast reads).  No shuffles.
+// one (sequence, KV head).  Its key and value tiles (32 KB each at head dim 128) are copied to
+// shared memory by 16-byte asynchronous copies issued before anything else, so the whole 64 KB is in
+// flight at once; a warp takes 32 tokens, one token per lane, and half of the group's query heads.
+//   scores : the lane reads ITS token's key row from shared memory (rows padded by 16 bytes: no bank
+//            conflicts) and multiplies it with the scaled query rows, which sit in shared memory as
+//            fp32 (broadcast reads).  No shuffles.
 //   softmax: per query head, maximum and sum over the warp's 32 tokens by butterfly; probabilities
 //            go to shared memory.
 //   values : lanes now own head-dim slices (coalesced 256-byte rows) and accumulate
@@ -30,7 +33,7 @@
 
 namespace mt {
 
-constexpr int kAttnSplitTokens = 128;  // tokens per CTA: four warps x 32 lanes
+constexpr int kAttnSplitTokens = 128;  // tokens per CTA: four groups of 32 lanes
 constexpr int kAttnMaxGroup = 8;       // query heads per KV head
 
 struct AttentionParams {
@@ -44,113 +47,168 @@ struct AttentionParams {
     float scale;
 };
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* global_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(smem_dst)), "l"(global_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
+constexpr int kAttnThreads = 256;
+constexpr int kAttnKeyPad = 8;  // bf16 elements: a key row in shared memory is 16 bytes longer than in the cache
+
+template <int kD>
+constexpr int attention_smem_bytes() {
+    return kAttnSplitTokens * (kD + kAttnKeyPad) * 2 + kAttnSplitTokens * kD * 2;
+}
+
+// Eight warps: warp w works on tokens [32 (w % 4), +32) of the split and on the query heads of half
+// w / 4 of the group (the first (G+1)/2 heads or the rest), so a tile in shared memory is read by two
+// warps and the FMAs of a token are shared between them.
 template <int kD, int kG>
-__global__ void __launch_bounds__(128) attention_decode_split_kernel(const AttentionParams p) {
+__global__ void __launch_bounds__(kAttnThreads) attention_decode_split_kernel(const AttentionParams p) {
     constexpr int kPerLane = kD / 32;  // head-dim elements a lane owns in the value phase (2 or 4)
     constexpr int kGPad = 8;
+    constexpr int kFirstHalf = (kG + 1) / 2;
+    constexpr int kKeyRow = kD + kAttnKeyPad;  // elements; 16 bytes of padding make lane-per-token reads conflict-free
+    extern __shared__ __align__(16) uint16_t tiles[];
+    uint16_t* key_tile = tiles;                               // [128][kD + 8]
+    uint16_t* value_tile = tiles + kAttnSplitTokens * kKeyRow;  // [128][kD]
     __shared__ __align__(16) float q_shared[kG][kD];
     __shared__ __align__(16) float prob[4][32][kGPad];
     __shared__ float warp_max[4][kG], warp_sum[4][kG];
-    __shared__ __align__(16) float warp_out[4][kG][kD];
+    // The four token groups' outputs reuse the key tile once every warp is done with it.
+    float* warp_out = reinterpret_cast<float*>(key_tile);     // [4][kG][kD]
+    static_assert(4 * kG * kD * 4 <= kAttnSplitTokens * kKeyRow * 2, "warp outputs fit the key tile");
 
     const int split = blockIdx.x;
     const int bh = blockIdx.y;                     // b * Hkv + h
     const int b = bh / p.kv_heads, h = bh - b * p.kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = warp & 3, half = warp >> 2;
+    const int g_begin = half == 0 ? 0 : kFirstHalf;
+    const int g_end = half == 0 ? kFirstHalf : kG;
     ptx::griddep_launch_dependents();
     ptx::griddep_wait();                           // q and the newest cache row are the preceding kernels' output
     const int n = p.lengths ? p.lengths[b] : p.tokens;
     const size_t cache_row0 = ((size_t)bh * p.capacity) * kD;
+    const int split_first = split * kAttnSplitTokens;
+    const int rows = min(kAttnSplitTokens, n - split_first);  // tokens of this split in use (<= 0: none)
+
+    // Both tiles are requested at once, 16 bytes per copy: every byte this CTA will read is in flight
+    // before any arithmetic starts.  Two groups, so the score phase can begin when the keys are in.
+    constexpr int kChunks = kD / 8;
+    for (int c = threadIdx.x; c < rows * kChunks; c += kAttnThreads) {
+        const int row = c / kChunks, chunk = c - row * kChunks;
+        cp_async_16(key_tile + row * kKeyRow + chunk * 8, p.k + cache_row0 + (size_t)(split_first + row) * kD + chunk * 8);
+    }
+    cp_async_commit();
+    for (int c = threadIdx.x; c < rows * kChunks; c += kAttnThreads) {
+        const int row = c / kChunks, chunk = c - row * kChunks;
+        cp_async_16(value_tile + row * kD + chunk * 8, p.v + cache_row0 + (size_t)(split_first + row) * kD + chunk * 8);
+    }
+    cp_async_commit();
 
     // Scaled queries of this KV head's group, fp32 (the cast comes before the scale multiplies).
-    for (int idx = threadIdx.x; idx < kG * kD; idx += 128) {
+    for (int idx = threadIdx.x; idx < kG * kD; idx += kAttnThreads) {
         const int g = idx / kD, d = idx - g * kD;
         const size_t at = ((size_t)b * p.q_heads + (size_t)h * kG + g) * kD + d;
         q_shared[g][d] = bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.q + at)) * p.scale;
     }
+    cp_async_wait<1>();
     __syncthreads();
 
-    const int token = split * kAttnSplitTokens + warp * 32 + lane;
-    const bool valid = token < n;
-    const int first = split * kAttnSplitTokens + warp * 32;
-    const int count = min(32, n - first);          // tokens of this warp in use (<= 0: none)
+    const int local = group * 32 + lane;           // this lane's token inside the split
+    const bool valid = local < rows;
+    const int first = group * 32;
+    const int count = min(32, rows - first);       // tokens of this warp in use (<= 0: none)
 
     // ---------------------------------------------------------------- scores: one token per lane
-    float score[kG];
+    float score[kFirstHalf];
 #pragma unroll
-    for (int g = 0; g < kG; ++g) score[g] = 0.0f;
+    for (int j = 0; j < kFirstHalf; ++j) score[j] = 0.0f;
     if (valid) {
-        const uint16_t* key = p.k + cache_row0 + (size_t)token * kD;
+        const uint16_t* key = key_tile + local * kKeyRow;
 #pragma unroll 4
         for (int d0 = 0; d0 < kD; d0 += 8) {
-            const uint4 raw = ptx::ld_global_dependent_u4(key + d0);
+            const uint4 raw = *reinterpret_cast<const uint4*>(key + d0);
             const float kf[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
                                  bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
 #pragma unroll
-            for (int g = 0; g < kG; ++g) {
+            for (int j = 0; j < kFirstHalf; ++j) {
+                const int g = g_begin + j;
+                if (g >= g_end) break;
                 const float4 qa = *reinterpret_cast<const float4*>(&q_shared[g][d0]);
                 const float4 qb = *reinterpret_cast<const float4*>(&q_shared[g][d0 + 4]);
-                float s = score[g];
+                float s = score[j];
                 s = fmaf(qa.x, kf[0], s); s = fmaf(qa.y, kf[1], s); s = fmaf(qa.z, kf[2], s); s = fmaf(qa.w, kf[3], s);
                 s = fmaf(qb.x, kf[4], s); s = fmaf(qb.y, kf[5], s); s = fmaf(qb.z, kf[6], s); s = fmaf(qb.w, kf[7], s);
-                score[g] = s;
+                score[j] = s;
             }
         }
     }
     // ---------------------------------------------------------------- softmax over the warp's tokens
-    float block_max[kG], block_sum[kG];
+    float block_max[kFirstHalf], block_sum[kFirstHalf];
 #pragma unroll
-    for (int g = 0; g < kG; ++g) {
-        float m = valid ? score[g] : -INFINITY;
+    for (int j = 0; j < kFirstHalf; ++j) {
+        const int g = g_begin + j;
+        if (g >= g_end) break;
+        float m = valid ? score[j] : -INFINITY;
 #pragma unroll
         for (int offset = 16; offset >= 1; offset >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, offset));
-        const float e = valid ? __expf(score[g] - m) : 0.0f;
-        prob[warp][lane][g] = e;
-        block_max[g] = m;
-        block_sum[g] = warp_sum_xor(e);
+        const float e = valid ? __expf(score[j] - m) : 0.0f;
+        prob[group][lane][g] = e;
+        block_max[j] = m;
+        block_sum[j] = warp_sum_xor(e);
     }
-    __syncwarp();
+    cp_async_wait<0>();
+    __syncthreads();  // values have landed; every warp is done with the key tile and has written its probabilities
     // ---------------------------------------------------------------- values: lanes own head-dim slices
-    float acc[kG][kPerLane];
+    float acc[kFirstHalf][kPerLane];
 #pragma unroll
-    for (int g = 0; g < kG; ++g)
+    for (int j = 0; j < kFirstHalf; ++j)
 #pragma unroll
-        for (int e = 0; e < kPerLane; ++e) acc[g][e] = 0.0f;
+        for (int e = 0; e < kPerLane; ++e) acc[j][e] = 0.0f;
     if (count > 0) {
-        const uint16_t* value = p.v + cache_row0 + (size_t)first * kD + lane * kPerLane;
+        const uint16_t* value = value_tile + first * kD + lane * kPerLane;
 #pragma unroll 4
         for (int t = 0; t < count; ++t) {
             float vf[kPerLane];
             if constexpr (kPerLane == 4) {
-                uint2 raw;
-                asm volatile("ld.global.v2.u32 {%0,%1}, [%2];" : "=r"(raw.x), "=r"(raw.y) : "l"(value + (size_t)t * kD));
+                const uint2 raw = *reinterpret_cast<const uint2*>(value + t * kD);
                 vf[0] = bf16_lo(raw.x); vf[1] = bf16_hi(raw.x); vf[2] = bf16_lo(raw.y); vf[3] = bf16_hi(raw.y);
             } else {
-                uint32_t raw;
-                asm volatile("ld.global.u32 %0, [%1];" : "=r"(raw) : "l"(value + (size_t)t * kD));
+                const uint32_t raw = *reinterpret_cast<const uint32_t*>(value + t * kD);
                 vf[0] = bf16_lo(raw); vf[1] = bf16_hi(raw);
             }
-            const float4 pa = *reinterpret_cast<const float4*>(&prob[warp][t][0]);
-            const float4 pb = *reinterpret_cast<const float4*>(&prob[warp][t][4]);
+            const float4 pa = *reinterpret_cast<const float4*>(&prob[group][t][0]);
+            const float4 pb = *reinterpret_cast<const float4*>(&prob[group][t][4]);
             const float pg[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
 #pragma unroll
-            for (int g = 0; g < kG; ++g)
+            for (int j = 0; j < kFirstHalf; ++j) {
+                const int g = half == 0 ? j : kFirstHalf + j;   // a compile-time index in each branch of `half`
+                if (g >= g_end) break;
 #pragma unroll
-                for (int e = 0; e < kPerLane; ++e) acc[g][e] = fmaf(pg[g], vf[e], acc[g][e]);
+                for (int e = 0; e < kPerLane; ++e) acc[j][e] = fmaf(half == 0 ? pg[j] : pg[(kFirstHalf + j) & 7], vf[e], acc[j][e]);
+            }
         }
     }
-    // ---------------------------------------------------------------- merge the four warps, in order
+    // ---------------------------------------------------------------- merge the four token groups, in order
 #pragma unroll
-    for (int g = 0; g < kG; ++g) {
+    for (int j = 0; j < kFirstHalf; ++j) {
+        const int g = g_begin + j;
+        if (g >= g_end) break;
         if (lane == 0) {
-            warp_max[warp][g] = block_max[g];
-            warp_sum[warp][g] = block_sum[g];
+            warp_max[group][g] = block_max[j];
+            warp_sum[group][g] = block_sum[j];
         }
 #pragma unroll
-        for (int e = 0; e < kPerLane; ++e) warp_out[warp][g][lane * kPerLane + e] = acc[g][e];
+        for (int e = 0; e < kPerLane; ++e) warp_out[(group * kG + g) * kD + lane * kPerLane + e] = acc[j][e];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < kG * kD; idx += 128) {
+    for (int idx = threadIdx.x; idx < kG * kD; idx += kAttnThreads) {
         const int g = idx / kD, d = idx - g * kD;
         float m = warp_max[0][g];
 #pragma unroll
@@ -160,7 +218,7 @@ __global__ void __launch_bounds__(128) attention_decode_split_kernel(const Atten
         for (int w = 0; w < 4; ++w) {
             const float factor = warp_max[w][g] == -INFINITY ? 0.0f : __expf(warp_max[w][g] - m);
             total = fmaf(warp_sum[w][g], factor, total);
-            value = fmaf(warp_out[w][g][d], factor, value);
+            value = fmaf(warp_out[(w * kG + g) * kD + d], factor, value);
         }
         if (p.splits == 1) {
             const size_t at = ((size_t)b * p.q_heads + (size_t)h * kG + g) * kD + d;
@@ -210,9 +268,19 @@ inline size_t attention_workspace_bytes(int batch, int q_heads, int tokens, int 
 
 template <int kD, int kG>
 inline int launch_attention_instance(const AttentionParams& params, int batch, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 64 || !configured[device]) {
+        if (cudaFuncSetAttribute(attention_decode_split_kernel<kD, kG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 attention_smem_bytes<kD>()) != cudaSuccess)
+            return MT_ERR_LAUNCH;
+        if (device < 64) configured[device] = true;
+    }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(params.splits, batch * params.kv_heads, 1);
-    config.blockDim = dim3(128, 1, 1);
+    config.blockDim = dim3(kAttnThreads, 1, 1);
+    config.dynamicSmemBytes = attention_smem_bytes<kD>();
     config.stream = stream;
     cudaLaunchAttribute attrs[1];
     attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -223,6 +291,7 @@ inline int launch_attention_instance(const AttentionParams& params, int batch, c
     if (params.splits > 1) {
         config.gridDim = dim3(batch * params.q_heads, 1, 1);
         config.blockDim = dim3(kD, 1, 1);
+        config.dynamicSmemBytes = 0;
         if (cudaLaunchKernelEx(&config, attention_decode_merge_kernel<kD>, params, kG) != cudaSuccess)
             return MT_ERR_LAUNCH;
     }

@@ -57,6 +57,32 @@ class QuantizedLinear(nn.Module):
         return out if self.bias is None else out + self.bias
 
 
+class QuantizedEmbedding(nn.Module):
+    """Token embedding stored as affine INT4 rows (MLX's nn.QuantizedEmbedding: weight uint32
+    [V, H/8], scales / biases [V, H/64]).  A lookup gathers the packed rows of the tokens and
+    dequantises just those (w = scale * q + bias in fp32, one rounding to the scales' dtype);
+    `as_linear()` serves the same triple as the tied output projection."""
+
+    def __init__(self, weight, scales, biases, *, group_size=64, bits=4):
+        super().__init__()
+        self.register_buffer("weight", weight)
+        self.register_buffer("scales", scales)
+        self.register_buffer("biases", biases)
+        self.group_size, self.bits, self.mode = group_size, bits, "affine"
+
+    def forward(self, tokens):
+        flat = tokens.reshape(-1)
+        packed = self.weight.view(torch.int32)[flat]                       # [T, H/8]
+        shifts = torch.arange(0, 32, 4, device=packed.device, dtype=torch.int32)
+        q = ((packed[..., None] >> shifts) & 15).reshape(flat.shape[0], -1).float()   # [T, H]
+        scales = self.scales[flat].float().repeat_interleave(self.group_size, dim=1)
+        biases = self.biases[flat].float().repeat_interleave(self.group_size, dim=1)
+        return (q * scales + biases).to(self.scales.dtype).reshape(*tokens.shape, -1)
+
+    def as_linear(self):
+        return QuantizedLinear(self.weight, self.scales, self.biases, group_size=self.group_size, bits=self.bits)
+
+
 class RMSNorm(nn.Module):
     def __init__(self, weight, eps=1e-6):
         super().__init__()
@@ -200,8 +226,9 @@ class TinyCausalLM(nn.Module):
 
 
 def random_model(seed=0, *, hidden=256, intermediate=512, heads=4, kv_heads=2, head_dim=64, layers=2, vocab=512,
-                 rope_theta=1e6, eps=1e-6, device="cuda"):
-    """A seeded random-init decoder-only model in the Qwen2.5 / Llama layout with 4-bit projections."""
+                 rope_theta=1e6, eps=1e-6, device="cuda", quantized_embedding=False, tie_word_embeddings=False):
+    """A seeded random-init decoder-only model in the Qwen2.5 / Llama layout with 4-bit projections
+    (and, when asked, a 4-bit embedding, optionally tied to the output projection)."""
     from .. import synth
 
     def linear(offset, fan_in, fan_out):
@@ -219,6 +246,11 @@ def random_model(seed=0, *, hidden=256, intermediate=512, heads=4, kv_heads=2, h
                                    RMSNorm(synth.norm_weight(seed * 1000 + base + 9, hidden, device), eps), mlp))
     generator = torch.Generator().manual_seed(seed * 1000 + 999)
     table = (torch.randn((vocab, hidden), generator=generator) / math.sqrt(hidden) * 4).to(torch.bfloat16)
-    embed = nn.Embedding.from_pretrained(table.to(device), freeze=True)
-    return TinyCausalLM(embed, blocks, RMSNorm(synth.norm_weight(seed * 1000 + 998, hidden, device), eps),
-                        linear(997, hidden, vocab), vocab)
+    if quantized_embedding or tie_word_embeddings:
+        from . import checkpoint
+
+        embed = QuantizedEmbedding(*(t.to(device) for t in checkpoint.quantize_affine(table)))
+    else:
+        embed = nn.Embedding.from_pretrained(table.to(device), freeze=True)
+    head = embed.as_linear() if tie_word_embeddings else linear(997, hidden, vocab)
+    return TinyCausalLM(embed, blocks, RMSNorm(synth.norm_weight(seed * 1000 + 998, hidden, device), eps), head, vocab)

@@ -343,3 +343,36 @@ def test_attention_patch_replaces_the_module_level_primitive_and_restores_it():
     with torch_lm.apply_metile_to_torch_lm(FakeLM(), attention=True, rms_norm=False, graph_fusion=False,
                                            quantized_mlp=False) as patch:
         assert "no attention surface" in patch.refusals["attention"]
+
+
+def test_autotune_argument_checks_and_cpu_run():
+    """On the CPU every patched call refuses and falls back to the model's own code, so every subset
+    reproduces the unpatched model exactly; the harness still compares, times and reports them."""
+    from metile_b200.integrations import autotune, blocks
+
+    with pytest.raises(TypeError):
+        autotune.autotune_metile_for_torch_lm(object(), torch.zeros((1, 4), dtype=torch.long))
+    lm = FakeLM()
+    with pytest.raises(ValueError):
+        autotune.autotune_metile_for_torch_lm(lm, torch.zeros((4,), dtype=torch.long))
+    with pytest.raises(ValueError):
+        autotune.autotune_metile_for_torch_lm(lm, torch.zeros((1, 4), dtype=torch.long), decode_steps=0)
+    assert blocks.DecoderBlock.forward.__name__ == "forward"  # nothing left patched by the refusals above
+
+
+def test_compare_decodes_accepts_ties_and_rejects_real_divergence():
+    from metile_b200.integrations.autotune import compare_decodes
+
+    logits = torch.tensor([[[5.0, 4.999, 0.0]], [[1.0, 9.0, 0.0]]])       # step 0 is a near tie, step 1 is not
+    same = ([[0], [1]], logits)
+    assert compare_decodes(same, same, 1e-2)[:3] == (True, "", True)
+    tie = ([[1], [1]], logits.clone())                                     # diverges at generated[0], a tie
+    valid, reason, match, at, _ = compare_decodes(same, tie, 1e-2)
+    assert valid and not match and at == 0
+    real = ([[0], [2]], logits.clone())                                    # diverges where the margin is 8
+    valid, reason, match, at, _ = compare_decodes(same, real, 1e-2)
+    assert not valid and at == 1 and "not a tie" in reason
+    off = (same[0], logits + torch.tensor(1.0))
+    valid, reason, *_ = compare_decodes(same, off, 1e-2)
+    assert not valid and "logits differ" in reason
+    assert not compare_decodes(same, (same[0], logits * float("nan")), 1e-2)[0]
