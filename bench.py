@@ -261,6 +261,10 @@ class Timer:
         torch.cuda.synchronize()
         return graph
 
+    def warm(self, graph):
+        """One untimed replay on the timer's stream, finished before anything else is queued."""
+        self.replay_seconds(graph, 1)
+
     def replay_seconds(self, graph, replays):
         torch = self.torch
         with torch.cuda.stream(self.stream):
@@ -310,8 +314,7 @@ def other_workloads(torch, device, timer, hbm_peak):
 
     def per_call(fn, calls_in_fn):
         graph = timer.capture(fn, 4)
-        graph.replay()
-        torch.cuda.synchronize()
+        timer.warm(graph)
         return summarise([timer.replay_seconds(graph, 1) / (4 * calls_in_fn) for _ in range(ROUNDS)])
 
     def with_rates(stats, bytes_per_call):
@@ -455,6 +458,15 @@ def other_workloads(torch, device, timer, hbm_peak):
                 launches[key] = count_kernels(one_decode)
                 if patched:
                     results["refusals"] = dict(handle.refusals)
+                    # The same patched step replayed as a CUDA graph: what the kernels take without the
+                    # interpreter between them (the eager numbers above are bound by Python dispatch).
+                    try:
+                        graph = timer.capture(decode_step, 1)
+                        timer.warm(graph)
+                        replays = [timer.replay_seconds(graph, 1) / block_copies for _ in range(ROUNDS)]
+                        results["decode_16_rows_kv2048"]["patched_graph_replay"] = summarise(replays)
+                    except Exception as error:  # capture is a convenience of the harness, not of the library
+                        results["decode_16_rows_kv2048"]["patched_graph_replay"] = {"unavailable": str(error)[:200]}
             finally:
                 if handle is not None:
                     handle.restore()
@@ -468,8 +480,47 @@ def other_workloads(torch, device, timer, hbm_peak):
     decode["patched_GBps"] = (block_bytes + kv_bytes) / (decode["patched"]["median_us"] * 1e-6) / 1e9
     decode["patched_frac_of_hbm"] = decode["patched_GBps"] / hbm_peak
     decode["gpu_kernels_per_decode_step"] = launches
+    replay = decode.get("patched_graph_replay", {})
+    if "median_us" in replay:
+        decode["patched_graph_GBps"] = (block_bytes + kv_bytes) / (replay["median_us"] * 1e-6) / 1e9
+        decode["patched_graph_frac_of_hbm"] = decode["patched_graph_GBps"] / hbm_peak
     results["timing"] = "eager launches, CUDA events (the unpatched block runs torch operators)"
     out["qwen2.5-1.5b_decoder_block"] = results
+    del block_list, decode_caches, model
+    torch.cuda.empty_cache()
+
+    # ---- output projection at vocabulary size: N = 128256, K = 2048 (Llama-3.2-1B lm_head) -------------
+    vocabulary, width = 128256, 2048
+    heads_w = [synth.affine_weight(980 + i, vocabulary, width, device) for i in range(2)]  # 2 x 148 MB
+    lm_head = []
+    for m in (1, 16):
+        xm = synth.activations(9, m, width, device, std=0.5)
+
+        def project(xm=xm):
+            for w in heads_w:
+                B.mlx_affine_qmv(xm, *w)
+
+        lm_head.append({"rows": m, **with_rates(per_call(project, 2),
+                                                vocabulary * width * (0.5 + 4 / 64) + m * width * 2 + m * vocabulary * 2)})
+    out["int4_lm_head_k2048_n128256"] = lm_head
+    del heads_w
+
+    # ---- feature plan of a four-layer model at the block's shape, chosen by timing its decode loop -------
+    from metile_b200.integrations import autotune
+
+    lm = blocks.random_model(seed=21, hidden=1536, intermediate=8960, heads=12, kv_heads=2, head_dim=128, layers=4,
+                             vocab=32768, device=device, tie_word_embeddings=True)
+    prompt = torch.randint(1, 32768, (1, 32), generator=torch.Generator().manual_seed(3)).to(device)
+    plan = autotune.autotune_metile_for_torch_lm(lm, prompt, decode_steps=8, trials=5)
+    chosen = next((m for m in plan.report.measurements if m.plan == plan), None)
+    out["feature_plan_4_layers_1536_8960"] = {
+        "selected": [name for name, on in plan.flags.items() if on],
+        "unpatched_us_per_token": plan.report.baseline_seconds_per_token * 1e6,
+        "selected_us_per_token": None if chosen is None else chosen.seconds_per_token * 1e6,
+        "subsets_measured": len(plan.report.measurements),
+        "subsets_rejected": [m.reason for m in plan.report.measurements if not m.valid],
+        "timing": "eager decode loop, batch 1, 8 steps, median of 5 interleaved rounds",
+    }
     return out
 
 
@@ -549,56 +600,56 @@ def run_ours(args):
         return float(t.item())
 
     # ---- headline: K steps, each one sweep ------------------------------------------------------------
-    # Single GPU: the sweep replayed as a CUDA graph.  Tensor-parallel: eager launches (a graph that
-    # contains the NCCL all-reduce is not replayed here).
+    # The sweep is replayed as a CUDA graph, on one GPU and tensor-parallel alike: the sum over the ranks
+    # is the library's own kernel (its call counter lives on the device), so every rank replays the same
+    # graph and no NCCL call sits inside it.
     log("weights resident; warm-up")
     for _ in range(3):
         sweep_once()
     torch.cuda.synchronize()
-    if tp:
-        run_steps = lambda n: timer.eager_seconds(sweep_once, n)  # noqa: E731
-    else:
-        step_graph = timer.capture(sweep_once, 1)
-        run_steps = lambda n: timer.replay_seconds(step_graph, n)  # noqa: E731
+    barrier()
+    step_graph = timer.capture(sweep_once, 1)
+    run_steps = lambda n: timer.replay_seconds(step_graph, n)  # noqa: E731
     run_steps(max(args.warmup, 3))
     barrier()
     with ClockSampler(local_rank) as clocks:
         seconds = run_steps(args.steps)
         barrier()
-        # Keep the sampler alive long enough for a few samples when the steps are very short.
-        if seconds < 0.5 and not tp:
+        seconds = max_over_ranks(seconds)
+        # Keep the sampler alive long enough for a few samples when the steps are very short.  The number
+        # of extra replays comes from the rank-agreed time: every rank must launch the same number of
+        # exchange kernels.
+        if seconds < 0.5:
             run_steps(max(1, int(0.5 / max(seconds / args.steps, 1e-6))))
-    seconds = max_over_ranks(seconds)
     step_seconds = seconds / args.steps
     total_bytes = per_mlp_bytes * len(sweep)
     value = total_bytes / step_seconds / 1e9
     log(f"headline: {step_seconds * 1e3:.3f} ms per step")
 
+    def check_device(where):
+        """Stop at once if a bounded device-side wait gave up (ranks out of step would otherwise spend
+        the wait limit on every later exchange)."""
+        ok, words = _lib.device_status()
+        if not ok:
+            raise SystemExit(f"a device-side wait gave up {where}: status words {[hex(w) for w in words]}")
+
+    check_device("during the headline steps")
+
     # ---- per-M detail: interleaved rounds, median and minimum -------------------------------------------
     def detail_for(flags=0):
-        if tp:
-            samples = {}
-            for m in sweep:
-                x, r = inputs[m]
+        graphs = {}
+        for m in sweep:
+            x, r = inputs[m]
 
-                def one(x=x, r=r):
-                    next_executor()(x, r)
+            def one(x=x, r=r):
+                next_executor()(x, r)
 
-                timer.eager_seconds(one, 8)
-                barrier()
-                samples[m] = [max_over_ranks(timer.eager_seconds(one, 16) / 16) for _ in range(ROUNDS)]
-        else:
-            graphs = {}
-            for m in sweep:
-                x, r = inputs[m]
-
-                def one(x=x, r=r):
-                    next_executor()(x, r)
-
-                graphs[m] = timer.capture(one, 8)
-                graphs[m].replay()
-            torch.cuda.synchronize()
-            samples = timer.interleaved_rounds(graphs, 8)
+            graphs[m] = timer.capture(one, 8)
+            timer.warm(graphs[m])
+        barrier()
+        samples = timer.interleaved_rounds(graphs, 8)
+        if tp:  # the slowest rank of every round
+            samples = {m: [max_over_ranks(v) for v in values] for m, values in samples.items()}
         rows = []
         for m in sweep:
             stats = summarise(samples[m])
@@ -623,6 +674,7 @@ def run_ours(args):
 
     log("per-M detail")
     detail = detail_for()
+    check_device("during the per-M rounds")
     sweep_invariant = None
     if not tp:
         log("per-M detail, batch-invariant mode (one kernel family for every batch size)")
@@ -640,8 +692,7 @@ def run_ours(args):
 
         def per_launch_seconds(fn, launches_per_call):
             graph = timer.capture(fn, 16)
-            graph.replay()
-            torch.cuda.synchronize()
+            timer.warm(graph)
             return statistics.median([timer.replay_seconds(graph, 1) / (16 * launches_per_call) for _ in range(ROUNDS)])
 
         def entry(kernel, rows_served, seconds, algorithmic, traffic, profile, bound="hbm", flops=0.0):
@@ -726,8 +777,7 @@ def run_ours(args):
                 next_executor().partial(x, r)
 
             graph = timer.capture(shard_only, 8)
-            graph.replay()
-            torch.cuda.synchronize()
+            timer.warm(graph)
             shard_seconds = statistics.median([timer.replay_seconds(graph, 1) / 8 for _ in range(ROUNDS)])
             buffer = torch.empty((m, hidden), dtype=torch.bfloat16, device=device)
 
@@ -739,13 +789,20 @@ def run_ours(args):
             def nccl_only(buffer=buffer):
                 dist.all_reduce(buffer)
 
-            reduce_times = []
-            for call in (reduce_only, nccl_only):
-                buffer.zero_()
-                timer.eager_seconds(call, 8)
-                barrier()
-                reduce_times.append(max_over_ranks(
-                    statistics.median([timer.eager_seconds(call, 16) / 16 for _ in range(ROUNDS)])))
+            buffer.zero_()
+            reduce_only()
+            torch.cuda.synchronize()
+            barrier()
+            reduce_graph = timer.capture(reduce_only, 8)
+            timer.warm(reduce_graph)
+            barrier()
+            reduce_times = [max_over_ranks(statistics.median(
+                [timer.replay_seconds(reduce_graph, 1) / 8 for _ in range(ROUNDS)]))]
+            buffer.zero_()
+            timer.eager_seconds(nccl_only, 8)
+            barrier()
+            reduce_times.append(max_over_ranks(
+                statistics.median([timer.eager_seconds(nccl_only, 16) / 16 for _ in range(ROUNDS)])))
             reduce_seconds, nccl_seconds = reduce_times
             shard_seconds = max_over_ranks(shard_seconds)
             shard_detail.append({"rows": m, "shard_mlp_us": shard_seconds * 1e6, "all_reduce_us": reduce_seconds * 1e6,
@@ -889,7 +946,7 @@ def run_ours(args):
             "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_seconds * 1e3},
             "gpu_launches": launches_per_sweep * args.steps,
-            "timing": "eager launches, CUDA events" if tp else "CUDA-graph replay, CUDA events",
+            "timing": "CUDA-graph replay, CUDA events",
             "clocks": clocks.summary(),
         }
         print(json.dumps(line))

@@ -137,9 +137,8 @@ int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags);
 /* The fused MLP of mt_affine_mlp for callers that may not allocate device memory.
  * No counterpart in the reference project.
  * Some hosts of this library cannot call cudaMalloc on the path that runs the MLP: a serving loop
- * that forbids allocation after start-up because cudaMalloc synchronises the whole device, a
- * plugin that was handed a fixed arena and nothing else, or code running while a stream is being
- * captured, where allocation calls are errors.  For them the bf16 hidden activations [M, I] live
+ * that forbids allocation after start-up because cudaMalloc synchronises the whole device, or a
+ * plugin that was handed a fixed arena and nothing else.  For them the bf16 hidden activations [M, I] live
  * in an array compiled into the library (mt_affine_mlp_static_max_bytes() bytes, 4 MiB, held by
  * every GPU that loads the library until the process exits) instead of a caller workspace.  Inputs
  * and the output are still the caller's.  The call makes no cudaMalloc / cudaFree and uses no
@@ -147,7 +146,7 @@ int mt_affine_mlp_launches(int M, int H, int I, unsigned int flags);
  *   - Limit: M * I * 2 bytes must not exceed mt_affine_mlp_static_max_bytes(); larger problems are
  *     refused with -7 before anything is queued.  Use mt_affine_mlp with your own workspace then.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
- *     that device current).  Make that first call before beginning any stream capture.
+ *     that device current) and keeps it.
  *   - All calls share the one array and it keeps the last call's contents.  Nothing needs clearing:
  *     each call overwrites every element it later reads.  Two calls that overlap on the GPU (two
  *     streams, two host threads) race on the array; serialise them.
@@ -212,8 +211,13 @@ int mt_rope_kv_append(const void* q, const void* k, const void* v, long long row
  * ipc_handle_out.  The caller exchanges the handles between the processes by any host means and passes
  * all `world` of them, in rank order, to mt_peer_group_connect.  Every rank must call
  * mt_peer_all_reduce the same number of times with the same `elements` (bf16 elements, a multiple
- * of 8); `partial` and `out` may be the same buffer.  Before mt_peer_group_destroy the caller makes
- * sure (a host barrier) that no peer has a call in flight. */
+ * of 8); `partial` and `out` may be the same buffer.  The call number lives on the device (the
+ * kernel advances it), so a CUDA graph that contains the call can be replayed, every rank the same
+ * number of times.  Two calls on one group must never overlap on a GPU: issue them on one stream,
+ * or order the streams.  Ranks that fall out of step (one launches more calls than another) wait
+ * out the limit on every later call, or read a slot before it is rewritten: count the launches.
+ * Before mt_peer_group_destroy the caller makes sure (a host barrier) that no peer has a call in
+ * flight. */
 int mt_peer_group_create(int rank, int world, size_t slot_bytes, void** group_out,
                          void* ipc_handle_out);
 int mt_peer_group_connect(void* group, const void* ipc_handles);

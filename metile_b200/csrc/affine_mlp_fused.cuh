@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 affine_mlp_fused_kernel(const __grid_constant__ FusedMlpParams p) {
     constexpr int kShares = kM == 1 ? 4 : 2;  // weight-row shares in flight per warp
     extern __shared__ uint8_t fused_smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fused_smem_raw) + 127) & ~(uintptr_t)127);
+    uint8_t* smem = fused_smem_raw + ((128u - (ptx::smem_u32(fused_smem_raw) & 127u)) & 127u);  // stays a shared-memory address
     const int grid = gridDim.x, cta = blockIdx.x;
     const int H = p.H, I = p.I;
     const FusedMlpLayout lay = fused_mlp_layout(kM, H, I, grid);
@@ -614,7 +614,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 affine_mlp_fused_mma_kernel(const __grid_constant__ FusedMlpParams p) {
     extern __shared__ uint8_t fused_smem_raw[];
     // 1024-byte alignment: the swizzle pattern of the tensor-map boxes repeats every 1024 bytes.
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fused_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem = fused_smem_raw + ((1024u - (ptx::smem_u32(fused_smem_raw) & 1023u)) & 1023u);  // stays a shared-memory address
     const int grid = gridDim.x, cta = blockIdx.x;
     const int M = p.M, H = p.H, I = p.I;
     const FusedMlpLayout lay = fused_mlp_layout(kFusedMmaMaxRows, H, I, grid);

@@ -219,7 +219,9 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     using Cfg = UmmaConfig<kT, kMPad>;
     static_assert(!kSwiglu || kT == 2, "SwiGLU pairs a gate tile with an up tile");
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // Aligned by offsetting the array itself (not by rounding a generic address), so that the compiler
+    // still knows these are shared-memory addresses and emits shared loads and stores.
+    uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* ring = smem;
     uint8_t* ab = smem + Cfg::kRingBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kDataBytes);

@@ -149,6 +149,62 @@ static int static_hidden_address(void** out) {
     return MT_OK;
 }
 
+// ---- staging between page-locked host memory and the device with a kernel instead of a copy engine ----
+// A copy engine's turn between two kernels of a stream costs several microseconds of hand-over on
+// each side; a small kernel that reads (writes) the mapped host buffer itself is chained to its
+// neighbours by programmatic dependent launch like any other kernel.  Used for up to kStageKernelBytes
+// per copy; larger copies keep the copy engine, whose bandwidth then matters more than its latency.
+constexpr size_t kStageKernelBytes = 512u << 10;
+
+__global__ void __launch_bounds__(256) stage_copy_kernel(const uint4* src, uint4* dst, unsigned int vectors) {
+    ptx::griddep_launch_dependents();
+    ptx::griddep_wait();  // the destination may still be read, the source still be written, by the kernel before
+    const unsigned int base = blockIdx.x * 1024u + threadIdx.x;
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const unsigned int i = base + 256u * j;
+        if (i < vectors)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w)
+                         : "l"(src + i));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const unsigned int i = base + 256u * j;
+        if (i < vectors) dst[i] = v[j];
+    }
+}
+
+// The device's address of a page-locked, mapped host buffer, or null when `host` is anything else
+// (pageable memory must never be handed to a kernel).
+static void* device_view_of_host(const void* host) {
+    cudaPointerAttributes attributes;
+    if (cudaPointerGetAttributes(&attributes, host) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (attributes.type != cudaMemoryTypeHost) return nullptr;
+    return attributes.devicePointer;
+}
+
+// Copies `bytes` (a multiple of 16, both ends 16-byte aligned) with the kernel; false = not queued.
+static bool stage_with_kernel(const void* src, void* dst, size_t bytes, cudaStream_t stream) {
+    if (bytes == 0 || bytes % 16 || bytes > kStageKernelBytes || !aligned_to(src, 16) || !aligned_to(dst, 16)) return false;
+    const unsigned int vectors = (unsigned int)(bytes / 16);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((vectors + 1023) / 1024);
+    config.blockDim = dim3(256);
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, stage_copy_kernel, static_cast<const uint4*>(src), static_cast<uint4*>(dst),
+                              vectors) == cudaSuccess;
+}
+
 // ---- self-test kernels: make a bounded device-side wait run out, on purpose and harmlessly ----------
 constexpr unsigned int kWaitSelfTest = 0x7E1;
 
@@ -363,16 +419,26 @@ int mt_affine_mlp_host(const void* x_host, const void* residual_host, void* out_
     const bool adjacent = residual_host && (flags & MT_FLAG_HOST_PAIR) &&
                           static_cast<const char*>(residual_host) == static_cast<const char*>(x_host) + bytes &&
                           static_cast<char*>(residual_device) == static_cast<char*>(x_device) + bytes;
-    if (cudaMemcpyAsync(x_device, x_host, adjacent ? 2 * bytes : bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    // Page-locked, mapped host buffers are read and written by small kernels (see stage_copy_kernel);
+    // anything else, and large copies, go through the copy engine.
+    const size_t in_bytes = adjacent ? 2 * bytes : bytes;
+    const void* x_view = in_bytes <= kStageKernelBytes ? device_view_of_host(x_host) : nullptr;
+    if (!(x_view && stage_with_kernel(x_view, x_device, in_bytes, s)) &&
+        cudaMemcpyAsync(x_device, x_host, in_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
         return MT_ERR_LAUNCH;
-    if (residual_host && !adjacent &&
-        cudaMemcpyAsync(residual_device, residual_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
-        return MT_ERR_LAUNCH;
+    if (residual_host && !adjacent) {
+        const void* r_view = bytes <= kStageKernelBytes ? device_view_of_host(residual_host) : nullptr;
+        if (!(r_view && stage_with_kernel(r_view, residual_device, bytes, s)) &&
+            cudaMemcpyAsync(residual_device, residual_host, bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+            return MT_ERR_LAUNCH;
+    }
     const int rc = mt_affine_mlp(x_device, gate_w, gate_scales, gate_biases, up_w, up_scales, up_biases, down_w,
                                  down_scales, down_biases, residual_host ? residual_device : nullptr, workspace,
                                  workspace_bytes, out_device, M, H, I, group_size, bits, flags & ~MT_FLAG_HOST_PAIR,
                                  stream);
     if (rc != MT_OK) return rc;
+    void* out_view = bytes <= kStageKernelBytes ? device_view_of_host(out_host) : nullptr;
+    if (out_view && stage_with_kernel(out_device, out_view, bytes, s)) return MT_OK;
     return cudaMemcpyAsync(out_host, out_device, bytes, cudaMemcpyDeviceToHost, s) == cudaSuccess ? MT_OK : MT_ERR_LAUNCH;
 }
 

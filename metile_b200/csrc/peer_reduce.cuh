@@ -12,7 +12,10 @@
 // allocated by mt_peer_group_create and opened by the peers through CUDA IPC handles.  Calls alternate
 // between the two slot sets: a rank can only be two calls ahead of a peer after that peer has launched
 // the call in between, which in stream order means the peer finished reading the older set.
-// Flags hold the call number (monotonic), so nothing is ever reset.
+// Flags hold the call number (monotonic), so nothing is ever reset.  The call number itself lives on
+// the device: every CTA reads it after the wait for the preceding kernel, and the last CTA to finish
+// advances it, so a launch carries no per-call argument and a captured CUDA graph of it can be
+// replayed (every rank must replay the same number of launches, as it must make the same calls).
 //
 // No multicast objects and no TMA are involved: ordinary stores to peer addresses and ordinary loads
 // from local memory.  Every wait is bounded; a rank whose peer never arrives records the peer in
@@ -35,7 +38,6 @@ struct PeerGroup {
     int device;
     size_t slot_bytes;
     size_t flags_offset;
-    unsigned int calls;
     unsigned char* peers[kPeerMaxWorld];  // every rank's allocation as mapped in this process
     bool opened[kPeerMaxWorld];
     bool connected;
@@ -45,12 +47,12 @@ struct PeerReduceParams {
     const uint4* partial;
     uint4* out;
     unsigned char* peers[kPeerMaxWorld];
+    unsigned char* local;  // == peers[rank]
     int rank;
     int world;
     unsigned int vectors;  // 16-byte units of the message
-    unsigned int call;
     size_t slot_bytes;
-    size_t flags_offset;
+    size_t flags_offset;   // [world][kPeerMaxCtas] flags, then the call counter and the exit tickets
     unsigned long long limit_ns;
 };
 
@@ -72,8 +74,8 @@ __device__ __forceinline__ void accumulate_bf16x8(float* acc, const uint4& v) {
 
 __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(const PeerReduceParams p) {
     __shared__ int gave_up;
+    __shared__ unsigned int call_shared;
     __shared__ unsigned char* peers[kPeerMaxWorld];  // indexed at run time: kept out of the parameter space
-    const unsigned int set = p.call & 1u;
     const unsigned int per_cta = (p.vectors + gridDim.x - 1) / gridDim.x;
     const unsigned int begin = blockIdx.x * per_cta;
     const unsigned int end = min(begin + per_cta, p.vectors);
@@ -83,10 +85,14 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(const PeerRed
         for (int i = 0; i < kPeerMaxWorld; ++i)
             if (i == threadIdx.x) peers[i] = p.peers[i];
     }
-    __syncthreads();
-
-    // The partial is the output of the kernel before this one in the stream.
+    // The partial is the output of the kernel before this one in the stream; the call counter was
+    // advanced by the previous launch of this kernel.
     ptx::griddep_wait();
+    unsigned int* counter = reinterpret_cast<unsigned int*>(p.local + p.flags_offset) + kPeerMaxWorld * kPeerMaxCtas;
+    if (threadIdx.x == 0) call_shared = __ldcg(counter) + 1u;
+    __syncthreads();
+    const unsigned int call = call_shared;
+    const unsigned int set = call & 1u;
 
     // 1. push this CTA's part of the partial into slot `rank` of every peer
     const size_t mine = ((size_t)set * p.world + p.rank) * p.slot_bytes;
@@ -101,18 +107,18 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(const PeerRed
     if (peer < p.world && peer != p.rank) {
         unsigned int* theirs =
             reinterpret_cast<unsigned int*>(peers[peer] + p.flags_offset) + p.rank * kPeerMaxCtas + blockIdx.x;
-        st_release_sys(theirs, p.call);
+        st_release_sys(theirs, call);
 
         // 2. wait until that peer's CTA of the same index has pushed its part here
         const unsigned int* here =
             reinterpret_cast<const unsigned int*>(peers[p.rank] + p.flags_offset) + peer * kPeerMaxCtas + blockIdx.x;
         const unsigned long long start = ptx::global_timer_ns();
-        while ((int)(ld_acquire_sys(here) - p.call) < 0) {
+        while ((int)(ld_acquire_sys(here) - call) < 0) {
             if (ptx::global_timer_ns() - start > p.limit_ns) {
                 if (atomicCAS(&g_device_status[0], 0u, kPeerWaitCode) == 0u) {
                     g_device_status[1] = blockIdx.x;
                     g_device_status[2] = (unsigned int)peer;
-                    g_device_status[3] = p.call;
+                    g_device_status[3] = call;
                 }
                 gave_up = 1;
                 break;
@@ -120,29 +126,42 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(const PeerRed
         }
     }
     __syncthreads();
-    if (gave_up) return;
 
     // 3. add the slots in rank order (this rank's own partial takes its place in the order)
-    const unsigned char* slots = peers[p.rank] + (size_t)set * p.world * p.slot_bytes;
-    for (unsigned int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int source = 0; source < p.world; ++source) {
-            const uint4 v = source == p.rank
-                                ? p.partial[i]
-                                : __ldcg(reinterpret_cast<const uint4*>(slots + (size_t)source * p.slot_bytes) + i);
-            accumulate_bf16x8(acc, v);
+    if (!gave_up) {
+        const unsigned char* slots = peers[p.rank] + (size_t)set * p.world * p.slot_bytes;
+        for (unsigned int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int source = 0; source < p.world; ++source) {
+                const uint4 v = source == p.rank
+                                    ? p.partial[i]
+                                    : __ldcg(reinterpret_cast<const uint4*>(slots + (size_t)source * p.slot_bytes) + i);
+                accumulate_bf16x8(acc, v);
+            }
+            uint4 r;
+            r.x = pack_bf16x2(acc[0], acc[1]);
+            r.y = pack_bf16x2(acc[2], acc[3]);
+            r.z = pack_bf16x2(acc[4], acc[5]);
+            r.w = pack_bf16x2(acc[6], acc[7]);
+            p.out[i] = r;
         }
-        uint4 r;
-        r.x = pack_bf16x2(acc[0], acc[1]);
-        r.y = pack_bf16x2(acc[2], acc[3]);
-        r.z = pack_bf16x2(acc[4], acc[5]);
-        r.w = pack_bf16x2(acc[6], acc[7]);
-        p.out[i] = r;
+    }
+
+    // 4. the last CTA out advances the call counter (also after a wait that gave up: the peers count
+    //    launches, not successes)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int* tickets = counter + 1;
+        if (atomicAdd(tickets, 1u) == gridDim.x - 1) {
+            *tickets = 0u;
+            *counter = call;
+            __threadfence();
+        }
     }
 }
 
 inline size_t peer_group_bytes(int world, size_t slot_bytes) {
-    return 2 * (size_t)world * slot_bytes + (size_t)world * kPeerMaxCtas * sizeof(unsigned int);
+    return 2 * (size_t)world * slot_bytes + ((size_t)kPeerMaxWorld * kPeerMaxCtas + 4) * sizeof(unsigned int);
 }
 
 inline int launch_peer_reduce(PeerGroup* group, const void* partial, void* out, size_t elements,
@@ -155,10 +174,10 @@ inline int launch_peer_reduce(PeerGroup* group, const void* partial, void* out, 
     p.partial = static_cast<const uint4*>(partial);
     p.out = static_cast<uint4*>(out);
     for (int i = 0; i < kPeerMaxWorld; ++i) p.peers[i] = group->peers[i];
+    p.local = group->peers[group->rank];
     p.rank = group->rank;
     p.world = group->world;
     p.vectors = (unsigned int)(elements / 8);
-    p.call = ++group->calls;
     p.slot_bytes = group->slot_bytes;
     p.flags_offset = group->flags_offset;
     p.limit_ns = limit_ns;

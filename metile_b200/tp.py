@@ -37,7 +37,9 @@ class PeerAllReduce:
 
     Construction is collective: every rank allocates its receive buffer in the library, and the CUDA
     IPC handles are exchanged with `all_gather_object`.  `max_elements` bounds the message; larger
-    tensors are refused by the library (-7)."""
+    tensors are refused by the library (-7).  Every rank must make the same calls in the same order,
+    on one stream (calls of one group must not overlap on a GPU); a CUDA graph containing calls may be
+    replayed, the same number of times on every rank."""
 
     def __init__(self, device, rank, world, max_elements, *, group=None, limit_ms=1000):
         import torch.distributed as dist

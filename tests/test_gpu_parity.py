@@ -491,6 +491,11 @@ def test_host_buffer_mlp_entry_point(cuda_device):
     from_host(both[0], both[1], out)
     torch.cuda.synchronize()
     assert_bit_equal(out.to(cuda_device), on_device(x, res), "host entry point, paired buffer")
+    # Pageable host tensors are never handed to a kernel: they go through the copy engine.
+    pageable_out = torch.empty((rows, hidden), dtype=torch.bfloat16)
+    from_host(x.cpu(), res.cpu(), pageable_out)
+    torch.cuda.synchronize()
+    assert_bit_equal(pageable_out.to(cuda_device), on_device(x, res), "host entry point, pageable memory")
     with pytest.raises(ValueError):
         from_host(torch.empty((9, hidden), dtype=torch.bfloat16).pin_memory(), None,
                   torch.empty((9, hidden), dtype=torch.bfloat16).pin_memory())

@@ -1,6 +1,5 @@
 """GPU test of mt_affine_mlp_static, the fused MLP for callers that may not allocate device
-memory (allocation-free serving loops, plugins confined to a fixed arena, code inside a stream
-capture).  The entry point keeps the hidden activations in an array compiled into the library.
+memory (allocation-free serving loops, plugins confined to a fixed arena).  The entry point keeps the hidden activations in an array compiled into the library.
 
 Called through the C ABI with raw pointers, twice in a row with different shapes, and compared
 with mt_affine_mlp (caller-owned workspace) on the same inputs: the two must agree bit for bit,
