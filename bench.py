@@ -505,6 +505,31 @@ def other_workloads(torch, device, timer, hbm_peak):
     out["int4_lm_head_k2048_n128256"] = lm_head
     del heads_w
 
+    # ---- the 32B-shaped MLP (hidden 5120 / intermediate 27648) unsharded: the one-GPU point of the
+    # tensor-parallel series that `--gpus N` runs ---------------------------------------------------------
+    big_h, big_i = 5120, 27648
+    big_sets = [synth.mlp_weights(100, big_h, big_i, device) for _ in range(2)]  # 2 x 239 MB
+    sample = synth.activations(5, 1, big_h, device)
+    big_execs = [B.mlx_affine_mlp_executor(sample, *w[0], *w[1], *w[2], sample) for w in big_sets]
+    big_bytes = 3 * big_h * big_i * (0.5 + 4 / 64)
+    big_rows = []
+    for m in (1, 16, 128):
+        xm = synth.activations(6, m, big_h, device)
+        rm = synth.activations(7, m, big_h, device)
+
+        def big_mlp(xm=xm, rm=rm):
+            for execute in big_execs:
+                execute(xm, rm)
+
+        big_rows.append({"rows": m, **with_rates(per_call(big_mlp, 2), big_bytes + 3 * m * big_h * 2)})
+    sweep_us = sum(r["median_us"] for r in big_rows)
+    out["qwen2.5-32b_mlp_5120_27648_one_gpu"] = {
+        "per_rows": big_rows, "sweep_ms": sweep_us * 1e-3,
+        "value_GBps": 3 * big_bytes / (sweep_us * 1e-6) / 1e9,
+        "note": "same sweep M = 1, 16, 128 and the same value definition as the tensor-parallel runs (--gpus N)"}
+    del big_sets, big_execs
+    torch.cuda.empty_cache()
+
     # ---- feature plan of a four-layer model at the block's shape, chosen by timing its decode loop -------
     from metile_b200.integrations import autotune
 

@@ -74,11 +74,17 @@ struct UmmaConfig {
     static constexpr int kWTileBytes = kUmmaTileRows * 128;         // one packed tile, four k-blocks
     static constexpr int kSlotBytes = kT * kWTileBytes;
     static constexpr int kBBytes = kMPad * 128;                     // activation tile of one k-block
-    static constexpr int kAbBytes = kBBytes;                        // operand bytes per stage in shared memory (A lives in tensor memory)
-    // Four operand stages.  A ring of activation tiles of its own, eight k-blocks ahead of the A
-    // stages, was measured and was slower (617 against 559 cycles per k-block at 16 rows): the extra
-    // wait and commit per k-block in the issuing threads cost more than the earlier request saved.
-    static constexpr int kAbStages = 4;
+    // A hand-off between the dequant warps and the MMA issuers covers kPair k-blocks: the waits,
+    // fences and arrivals of a hand-off cost about as many instructions as dequantising one k-block, so
+    // sharing them between two k-blocks shortens the instruction stream that bounds the kernel.
+    static constexpr int kPair = 2;
+    static constexpr int kPairsPerSlot = kUmmaKBlocksPerSlot / kPair;
+    static constexpr int kAbBytes = kPair * kBBytes;                // activation bytes per stage in shared memory (A lives in tensor memory)
+    // One operand stage per depth group.  A ring of activation tiles of its own, eight k-blocks ahead
+    // of the A stages, was measured and was slower (617 against 559 cycles per k-block at 16 rows): the
+    // extra wait and commit per k-block in the issuing threads cost more than the earlier request saved.
+    static constexpr int kAbStages = kDepth;
+    static constexpr int kRingReaders = kT == 2 ? kDequantWarps : kDequantWarps / 2;  // warps that read one ring slot
     // Two threads (in two warps) issue the MMAs.  One issuer's loop per k-block -- poll the operand
     // barrier (~140 cycles even when it is already complete), four MMAs whose issue blocks while the
     // pipe is busy, commit -- measured 566 cycles per k-block at 16 rows, more than twice what the
@@ -88,7 +94,7 @@ struct UmmaConfig {
     // epilogue adds (even + odd), an order that depends on K only.
     static constexpr int kAcc = kT == 1 ? 2 : 1;
     static constexpr int kAccCols = kT * kAcc * kMPad;
-    static constexpr int kATmemCols = kAbStages * kT * 32;
+    static constexpr int kATmemCols = kAbStages * kT * kPair * 32;
     static constexpr int kTmemCols = pow2_at_least(kAccCols + kATmemCols);
     // The ring takes what shared memory the footprint leaves, up to 8 slots.
     static constexpr int kBudgetBytes = 196 * 1024;
@@ -113,8 +119,8 @@ struct UmmaConfig {
     static_assert((kAllowedPerSm + 1) * kSmemBytes > 227 * 1024, "one CTA too many would fit on an SM");
     static_assert(kAllowedPerSm * (kSmemBytes + 1024) <= 227 * 1024, "the intended residency does not fit");
     static_assert(kAllowedPerSm * kTmemCols <= 512, "tensor memory over-subscribed");
-    static_assert(kAbStages % kDepth == 0, "each depth group owns whole operand stages");
-    static_assert(kUmmaKBlocksPerSlot % kDepth == 0, "a group sees the same k-blocks in every slot");
+    static_assert(kAbStages == kDepth, "each depth group owns one operand stage");
+    static_assert(kDepth % kPairsPerSlot == 0, "a group sees the same pair of k-blocks in every slot it reads");
 };
 
 struct UmmaParams {
@@ -189,23 +195,29 @@ __device__ __forceinline__ void umma_issue(uint32_t tmem_base, const uint8_t* ab
     constexpr int chain = kT == 2 ? 0 : kIssuer;      // its accumulator within the tile
     const uint32_t d_tmem = tmem_base + (t * Cfg::kAcc + chain) * kMPad;
     const uint64_t desc0 = ptx::smem_desc_k_major_sw128(ptx::smem_u32(ab));
-    for (int i0 = 0; i0 < nkb; i0 += Cfg::kAbStages) {
-        const uint32_t phase = (i0 / Cfg::kAbStages) & 1;
-        const uint32_t later = i0 > 0 ? 1u : 0u;
+    const int npairs = (nkb + Cfg::kPair - 1) / Cfg::kPair;
+    for (int p0 = 0; p0 < npairs; p0 += Cfg::kAbStages) {
+        const uint32_t phase = (p0 / Cfg::kAbStages) & 1;
+        const uint32_t later = p0 > 0 ? 1u : 0u;
 #pragma unroll
         for (int a = 0; a < Cfg::kAbStages; ++a) {
             if (kT == 1 && (a & 1) != kIssuer) continue;
-            const int i = i0 + a;
-            if (i >= nkb) break;
-            if (!ptx::mbar_wait_spin(&ab_full[a], phase, abort_flag, kWaitAbFull)) { i0 = nkb; break; }
+            const int pair = p0 + a;
+            if (pair >= npairs) break;
+            if (!ptx::mbar_wait_spin(&ab_full[a], phase, abort_flag, kWaitAbFull)) { p0 = npairs; break; }
             ptx::tc_fence_after_sync();
+            const int valid = nkb - pair * Cfg::kPair;  // k-blocks of this pair in range: 1 only at a ragged end
 #pragma unroll
-            for (int ks = 0; ks < kUmmaBlockK / 16; ++ks) {
-                const uint64_t b_desc = desc0 + (uint64_t)((a * Cfg::kAbBytes + ks * 32) >> 4);
-                // The first MMA into an accumulator overwrites it.
-                const uint32_t accumulate = (ks > 0 || a > (kT == 1 ? kIssuer : 0)) ? 1u : later;
-                const uint32_t a_tmem = tmem_base + Cfg::kAccCols + (a * kT + t) * 32 + ks * 8;
-                ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+            for (int kb = 0; kb < Cfg::kPair; ++kb) {
+                if (kb >= valid) break;
+#pragma unroll
+                for (int ks = 0; ks < kUmmaBlockK / 16; ++ks) {
+                    const uint64_t b_desc = desc0 + (uint64_t)((a * Cfg::kAbBytes + kb * Cfg::kBBytes + ks * 32) >> 4);
+                    // The first MMA into an accumulator overwrites it.
+                    const uint32_t accumulate = (kb > 0 || ks > 0 || a > (kT == 1 ? kIssuer : 0)) ? 1u : later;
+                    const uint32_t a_tmem = tmem_base + Cfg::kAccCols + ((a * kT + t) * Cfg::kPair + kb) * 32 + ks * 8;
+                    ptx::umma_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+                }
             }
             ptx::umma_commit(&ab_empty[a]);
         }
@@ -252,7 +264,7 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
     if (threadIdx.x == 0) {
         for (int i = 0; i < Cfg::kStages; ++i) {
             ptx::mbar_init(&ring_full[i], 1);
-            ptx::mbar_init(&ring_empty[i], Cfg::kDequantWarps);
+            ptx::mbar_init(&ring_empty[i], Cfg::kRingReaders);
         }
         for (int i = 0; i < Cfg::kAbStages; ++i) {
             ptx::mbar_init(&ab_full[i], Cfg::kWarpsPerKBlock + 1);  // dequant warps + the activation tile's copy
@@ -306,13 +318,16 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
             ptx::prefetch_tensor_map(&p.x_map);
             ptx::griddep_wait();  // the activations are the preceding kernel's output
             int issued = 0;
-            for (int i = 0; i < nkb; ++i) {
-                const int a = i % Cfg::kAbStages;
-                const uint32_t phase = (uint32_t)(i / Cfg::kAbStages) & 1u;
+            const int npairs = (nkb + Cfg::kPair - 1) / Cfg::kPair;
+            for (int pair = 0; pair < npairs; ++pair) {
+                const int a = pair % Cfg::kAbStages;
+                const uint32_t phase = (uint32_t)(pair / Cfg::kAbStages) & 1u;
                 if (!ptx::mbar_wait(&ab_empty[a], phase ^ 1u, abort_flag, kWaitAbEmpty)) break;
-                ptx::mbar_expect_tx(&ab_full[a], Cfg::kBBytes);
-                ptx::tma_load_2d(ab + a * Cfg::kAbBytes, &p.x_map, (kb_begin + i) * kUmmaBlockK, 0,
-                                 &ab_full[a]);
+                const int valid = min(Cfg::kPair, nkb - pair * Cfg::kPair);
+                ptx::mbar_expect_tx(&ab_full[a], (uint32_t)valid * Cfg::kBBytes);
+                for (int kb = 0; kb < valid; ++kb)
+                    ptx::tma_load_2d(ab + a * Cfg::kAbBytes + kb * Cfg::kBBytes, &p.x_map,
+                                     (kb_begin + pair * Cfg::kPair + kb) * kUmmaBlockK, 0, &ab_full[a]);
                 ++issued;
             }
             if (*abort_flag) {
@@ -336,52 +351,60 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
         const int n = min(n0 + r, p.N - 1);            // rows past N were zero-filled by TMA
         const uint16_t* scale_row = p.scales[t] + (size_t)n * kblocks + kb_begin;
         const uint16_t* bias_row = p.biases[t] + (size_t)n * kblocks + kb_begin;
-        uint32_t scale_next = 0, bias_next = 0;
-        if (depth < nkb) {
-            scale_next = ldg_nc_u16(scale_row + depth);
-            bias_next = ldg_nc_u16(bias_row + depth);
+        // This group's share: pair `pair_in_slot` of every `slot_step`-th ring slot, always into operand
+        // stage `depth`; its n-th hand-off uses phase n & 1 of that stage's barriers.
+        constexpr int kSlotStep = Cfg::kDepth / Cfg::kPairsPerSlot;
+        const int pair_in_slot = depth % Cfg::kPairsPerSlot;
+        const int slot_first = depth / Cfg::kPairsPerSlot;
+        const int a = depth;
+        uint32_t scale_next[Cfg::kPair], bias_next[Cfg::kPair];
+#pragma unroll
+        for (int kb = 0; kb < Cfg::kPair; ++kb) {
+            const int i = slot_first * kUmmaKBlocksPerSlot + pair_in_slot * Cfg::kPair + kb;
+            scale_next[kb] = i < nkb ? ldg_nc_u16(scale_row + i) : 0u;
+            bias_next[kb] = i < nkb ? ldg_nc_u16(bias_row + i) : 0u;
         }
-        bool alive = true;
-        for (int st = 0; st < nslots && alive; ++st) {
+        uint32_t use = 0;
+        for (int st = slot_first; st < nslots; st += kSlotStep, ++use) {
             const int s = st % Cfg::kStages;
             const uint32_t phase = (st / Cfg::kStages) & 1;
             const uint8_t* slot = ring + s * Cfg::kSlotBytes;
-            bool waited = false;
+            const int i0 = st * kUmmaKBlocksPerSlot + pair_in_slot * Cfg::kPair;  // first k-block of the pair
+            uint32_t scale_bits[Cfg::kPair], bias_bits[Cfg::kPair];
 #pragma unroll
-            for (int jj = 0; jj < kUmmaKBlocksPerSlot / Cfg::kDepth; ++jj) {
-                const int j = depth + jj * Cfg::kDepth;              // k-block inside the slot
-                const int i = st * kUmmaKBlocksPerSlot + j;          // k-block inside this CTA's range
-                if (i >= nkb) break;
-                const int a = i % Cfg::kAbStages;
-                const uint32_t aphase = (i / Cfg::kAbStages) & 1;
-                const uint32_t scale_bits = scale_next, bias_bits = bias_next;
-                if (i + Cfg::kDepth < nkb) {
-                    scale_next = ldg_nc_u16(scale_row + i + Cfg::kDepth);
-                    bias_next = ldg_nc_u16(bias_row + i + Cfg::kDepth);
+            for (int kb = 0; kb < Cfg::kPair; ++kb) {
+                scale_bits[kb] = scale_next[kb];
+                bias_bits[kb] = bias_next[kb];
+                const int following = i0 + kSlotStep * kUmmaKBlocksPerSlot + kb;
+                if (following < nkb) {
+                    scale_next[kb] = ldg_nc_u16(scale_row + following);
+                    bias_next[kb] = ldg_nc_u16(bias_row + following);
                 }
-                if (!waited) {
-                    if (!ptx::mbar_wait(&ring_full[s], phase, abort_flag, kWaitRingFull)) { alive = false; break; }
-                    waited = true;
-                }
-                if (!ptx::mbar_wait(&ab_empty[a], aphase ^ 1, abort_flag, kWaitAbEmpty)) { alive = false; break; }
+            }
+            if (!ptx::mbar_wait(&ring_full[s], phase, abort_flag, kWaitRingFull)) break;
+            if (i0 < nkb) {
+                if (!ptx::mbar_wait(&ab_empty[a], (use & 1u) ^ 1u, abort_flag, kWaitAbEmpty)) break;
                 __syncwarp();  // the .sync.aligned tcgen05 instructions below need a converged warp
                 ptx::tc_fence_after_sync();
-
-                // 32 B of this row for k-block j: 16-byte chunks 2j and 2j+1, XOR-swizzled by the row.
                 const uint8_t* wrow = slot + t * Cfg::kWTileBytes + r * 128;
-                const uint4 w_lo = *reinterpret_cast<const uint4*>(wrow + (((2 * j) ^ (r & 7)) << 4));
-                const uint4 w_hi = *reinterpret_cast<const uint4*>(wrow + (((2 * j + 1) ^ (r & 7)) << 4));
-                const __nv_bfloat162 scale2 = bits_bf162(scale_bits | (scale_bits << 16));
-                const __nv_bfloat162 bias2 = bits_bf162(bias_bits | (bias_bits << 16));
-                uint32_t wq[32];
-                const uint32_t words[8] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w, w_hi.x, w_hi.y, w_hi.z, w_hi.w};
 #pragma unroll
-                for (int c = 0; c < 8; ++c) dequant_word_bf16(words[c], scale2, bias2, &wq[4 * c]);
-
-                const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + Cfg::kAccCols +
-                                        (a * kT + t) * 32;
-                ptx::tmem_st16(a_tmem, &wq[0]);
-                ptx::tmem_st16(a_tmem + 16, &wq[16]);
+                for (int kb = 0; kb < Cfg::kPair; ++kb) {
+                    if (i0 + kb >= nkb) break;  // ragged end: the pair holds one k-block
+                    // 32 B of this row for k-block j: 16-byte chunks 2j and 2j+1, XOR-swizzled by the row.
+                    const int j = pair_in_slot * Cfg::kPair + kb;
+                    const uint4 w_lo = *reinterpret_cast<const uint4*>(wrow + (((2 * j) ^ (r & 7)) << 4));
+                    const uint4 w_hi = *reinterpret_cast<const uint4*>(wrow + (((2 * j + 1) ^ (r & 7)) << 4));
+                    const __nv_bfloat162 scale2 = bits_bf162(scale_bits[kb] | (scale_bits[kb] << 16));
+                    const __nv_bfloat162 bias2 = bits_bf162(bias_bits[kb] | (bias_bits[kb] << 16));
+                    uint32_t wq[32];
+                    const uint32_t words[8] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w, w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) dequant_word_bf16(words[c], scale2, bias2, &wq[4 * c]);
+                    const uint32_t a_tmem = tmem_base + ((uint32_t)((warp & 3) << 5) << 16) + Cfg::kAccCols +
+                                            ((a * kT + t) * Cfg::kPair + kb) * 32;
+                    ptx::tmem_st16(a_tmem, &wq[0]);
+                    ptx::tmem_st16(a_tmem + 16, &wq[16]);
+                }
                 // The ring slot read above with ordinary loads may later be overwritten by TMA (async
                 // proxy): order the two.  Releasing a slot without such a fence was observed to let the
                 // refill overtake the reads.
@@ -390,12 +413,6 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&ab_full[a]);
-            }
-            if (!alive) break;
-            if (!waited) {
-                // No k-block of this slot belongs to this group (ragged tail): still observe the
-                // refill before releasing, so the arrival is counted in the right phase.
-                if (!ptx::mbar_wait(&ring_full[s], phase, abort_flag, kWaitRingFull)) break;
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&ring_empty[s]);
@@ -418,7 +435,7 @@ affine_umma_kernel(const __grid_constant__ UmmaParams p) {
                 if (ok) {
 #pragma unroll
                     for (int chain = 0; chain < Cfg::kAcc; ++chain) {
-                        if (chain > 0 && nkb < 2) break;  // the odd k-blocks' accumulator was never written
+                        if (chain > 0 && nkb <= Cfg::kPair) break;  // the odd pairs' accumulator was never written
                         uint32_t part[16];
                         ptx::tmem_ld16(tmem_base + ((uint32_t)((warp & 3) << 5) << 16) +
                                            (t * Cfg::kAcc + chain) * kMPad + c0, part);
