@@ -49,7 +49,7 @@ ROUNDS = 25
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernel families, from the
 # ncu captures summarised in the named files under profiles/; None where no capture exists.
 PROFILE_K2 = "profiles/affine_umma_llama1b.md"
-TRAFFIC = {"swiglu_16": None, "down_16": None, "swiglu_128": None, "down_128": None}
+TRAFFIC = {"swiglu_16": 19019264, "down_16": 9845248, "swiglu_128": 19482880, "down_128": 12145408}
 
 
 def weight_bytes(hidden, intermediate):
@@ -744,9 +744,9 @@ def run_ours(args):
         packed = hidden * inter * (0.5 + 4 / 64)  # one projection: nibbles + bf16 scales and biases
         single_rows = [m for m in sweep if library.mt_affine_mlp_launches(m, hidden, inter, 0) == 1]
         for rows_served, label, traffic, profile in (
-                ([m for m in single_rows if m <= 1], "single-launch MLP on CUDA cores (affine_mlp_fused_kernel)", 28381952,
+                ([m for m in single_rows if m <= 1], "single-launch MLP on CUDA cores (affine_mlp_fused_kernel)", 28378368,
                  "profiles/affine_mlp_fused_m1_llama1b.md"),
-                ([m for m in single_rows if m > 1], "single-launch MLP on mma.sync (affine_mlp_fused_mma_kernel)", 28458496,
+                ([m for m in single_rows if m > 1], "single-launch MLP on mma.sync (affine_mlp_fused_mma_kernel)", 28456192,
                  "profiles/affine_mlp_fused_mma_m8_llama1b.md")):
             if not rows_served:
                 continue

@@ -9,7 +9,7 @@
 //   residual : bf16(bf16(acc) + residual)
 //   SwiGLU   : l = bf16(gate), r = bf16(up), y = 1/(1+exp(|l|)), sig = bf16(l<0 ? y : 1-y),
 //              out = bf16(bf16(l*sig) * r)
-// One warp produces kOut outputs for all rows of a pass; up to 32 rows share one pass over the matrix.
+// One warp produces kOut outputs for all rows of a pass; up to 16 rows share one pass over the matrix.
 #pragma once
 
 #include "common.cuh"
@@ -133,10 +133,11 @@ template <int kM, DenseEpilogue kEp>
 inline int launch_dense_m(const uint16_t* x, const uint16_t* w0, const uint16_t* w1, const uint16_t* residual,
                           uint16_t* out, int rows, int K, int N, int sm_count, cudaStream_t stream) {
     constexpr int kStreams = kEp == DenseEpilogue::kSwiglu ? 2 : 1;
-    // One output per warp and many warps: the fp32 order of an output is fixed (one warp, ascending
-    // blocks), so parallelism comes from the outputs.  Few rows: six blocks of weights in flight per warp.
-    constexpr int kOut = (kM * kStreams <= 4) ? 2 : 1;
-    constexpr int kAhead = kM * kStreams <= 8 ? (kOut == 2 ? 3 : 6) : 3;
+    // The fp32 order of an output is fixed (one warp, ascending blocks), so parallelism comes from the
+    // outputs.  Two outputs per warp share every activation load and conversion (measured at 8 rows:
+    // 17.3 us against 20.2 us with one output per warp); 32 rows x two outputs would not fit the registers.
+    constexpr int kOut = (kM * kStreams <= 16) ? 2 : 1;
+    constexpr int kAhead = kM * kStreams <= 4 ? 3 : 2;
     const int warps_needed = (N + kOut - 1) / kOut;
     int grid = (warps_needed + 7) / 8;
     const int cap = sm_count * 8;
@@ -155,10 +156,12 @@ inline int launch_dense(const void* x, const void* w0, const void* w1, const voi
     const uint16_t* bp = static_cast<const uint16_t*>(w1);
     const uint16_t* rp = static_cast<const uint16_t*>(residual);
     uint16_t* op = static_cast<uint16_t*>(out);
-    // Up to 32 rows share one pass over the weights (the reference's kernels stop at 31); larger
-    // batches run as chunks of 32, whose re-reads of the matrix come from L2 when it fits there.
-    // A row's result is the same in any chunking: its fp32 order depends on (K, lane) only.
-    constexpr int kChunk = kEp == DenseEpilogue::kSwiglu ? 16 : 32;
+    // Up to 16 rows share one pass over the weights; larger batches run as chunks of 16, whose
+    // re-reads of the matrix come from L2 when it fits there (measured at K = 1536, N = 8960: 26 us per
+    // 16-row pass against 92 us for a 32-row pass, whose 32 accumulators per output leave the FMA pipe
+    // waiting on activation loads).  A row's result is the same in any chunking: its fp32 order depends
+    // on (K, lane) only.
+    constexpr int kChunk = 16;
     for (int m0 = 0; m0 < M; m0 += kChunk) {
         const int rows = M - m0 < kChunk ? M - m0 : kChunk;
         const uint16_t* xc = xp + (size_t)m0 * K;
@@ -175,8 +178,7 @@ inline int launch_dense(const void* x, const void* w0, const void* w1, const voi
             case 7: rc_code = launch_dense_m<7, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
             case 8: rc_code = launch_dense_m<8, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream); break;
             default:
-                if (rows <= 16 || kChunk == 16) rc_code = launch_dense_m<16, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream);
-                else rc_code = launch_dense_m<kChunk, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream);
+                rc_code = launch_dense_m<16, kEp>(xc, ap, bp, rc, oc, rows, K, N, sm_count, stream);
                 break;
         }
         if (rc_code != MT_OK) return rc_code;
