@@ -148,14 +148,14 @@ def test_fused_decode_step_of_an_attention_module(cuda_device):
     keys[:, :, length] = OA.rope(k, positions, 1e6)
     attended = OA.attention_decode(OA.rope(q, positions, 1e6).reshape(batch, 12, 1, 128), keys, values, 128 ** -0.5)
     oracle_out = A.qmm(attended.reshape(batch, 1536), *triple(module.o_proj), weights="bf16")
-    assert_within(got.reshape(batch, 1536), oracle_out, rel=4e-3, what="fused decode step vs oracle composition")
+    assert_within(got.reshape(batch, 1536), oracle_out, rel=3e-3, what="fused decode step vs oracle composition")
     # With the residual in the output projection's epilogue.
     cache_res = filled_cache(module, batch, length, capacity, cuda_device)
     with torch.no_grad():
         with_residual = torch_lm.execute_attention_decode(module, x, cache_res, residual=residual)
     assert_within(with_residual.reshape(batch, 1536),
                   A.qmm(attended.reshape(batch, 1536), *triple(module.o_proj), residual=f32(residual.reshape(batch, 1536)),
-                        weights="bf16"), rel=4e-3, what="fused decode step + residual")
+                        weights="bf16"), rel=3e-3, what="fused decode step + residual")
 
 
 def test_patched_attention_surfaces_and_refusals(cuda_device):

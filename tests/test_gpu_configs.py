@@ -20,7 +20,6 @@ from oracle import cport
 from tests.helpers import assert_bit_equal, assert_within, f32, triple_np
 
 pytestmark = pytest.mark.gpu
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 RATIOS = {}
 
 
@@ -36,7 +35,7 @@ def record(name, ratio, rel):
 @pytest.fixture(scope="module", autouse=True)
 def write_ratio_table():
     yield
-    out = os.path.join(ROOT, "gpurun_out")
+    out = os.environ.get("METILE_REPORT_DIR", "")
     if RATIOS and os.path.isdir(out):
         with open(os.path.join(out, "parity_ratios.json"), "w") as handle:
             json.dump(RATIOS, handle, indent=1, sort_keys=True)

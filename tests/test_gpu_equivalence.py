@@ -25,7 +25,6 @@ from oracle import cport
 from tests.helpers import assert_bit_equal, assert_within
 
 pytestmark = pytest.mark.gpu
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TOLERANCE = 2e-2
 FEATURE_SETS = {
     "attention": dict(attention=True, rms_norm=False, graph_fusion=False, quantized_mlp=False),
@@ -50,7 +49,7 @@ def prompt(device, batch=2):
 @pytest.fixture(scope="module", autouse=True)
 def write_matrix():
     yield
-    out = os.path.join(ROOT, "gpurun_out")
+    out = os.environ.get("METILE_REPORT_DIR", "")
     if MATRIX and os.path.isdir(out):
         with open(os.path.join(out, "equivalence_matrix.json"), "w") as handle:
             json.dump(MATRIX, handle, indent=1, sort_keys=True)
@@ -98,7 +97,7 @@ def test_autotune_selects_a_verified_plan_and_caches_it(cuda_device):
     assert blocks.DecoderBlock.forward.__name__ == "forward", "the harness left a class patched"
     with plan.apply(model):
         autotune.greedy_decode(model, tokens, 2)
-    out = os.path.join(ROOT, "gpurun_out")
+    out = os.environ.get("METILE_REPORT_DIR", "")
     if os.path.isdir(out):
         with open(os.path.join(out, "autotune_report.txt"), "w") as handle:
             handle.write(text + "\n")

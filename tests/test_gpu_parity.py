@@ -93,7 +93,7 @@ def test_golden_residual_and_mlp(cuda_device, family):
         y = execute(x, res)
     np.testing.assert_allclose(f32(y), A.bf16_from_bits(kat[name + "_y"]), rtol=3e-2, atol=3e-2)
     triples_np = [golden_triple_np(kat, f"{name}_{part}") for part in ("gate", "up", "down")]
-    assert_within(y, A.mlp(f32(x), *triples_np, f32(res), weights=oracle_weights(family)), rel=4e-3)
+    assert_within(y, A.mlp(f32(x), *triples_np, f32(res), weights=oracle_weights(family)), rel=3e-3)
 
 
 @pytest.mark.parametrize("rows", [33, 65, 129])
@@ -163,28 +163,28 @@ def test_projection_variants_against_oracle(cuda_device, family, k, n):
 
 
 def test_config0_gemv_1536_8960(cuda_device):
-    """BASELINE config 0: M=1, K=1536, N=8960."""
+    """The single projection of a Qwen2.5-1.5B MLP: M=1, K=1536, N=8960."""
     k, n = 1536, 8960
     weight = synth.affine_weight(0, n, k, cuda_device)
     x = synth.activations(1, 1, k, cuda_device)
     weight_np = triple_np(weight)
     y = B.mlx_affine_qmv(x, *weight)
     assert y.shape == (1, n) and y.dtype == torch.bfloat16
-    assert_within(y, A.qmm(f32(x), *weight_np), what="config 0 (default dispatch)")
+    assert_within(y, A.qmm(f32(x), *weight_np), what="1536 -> 8960 projection (default dispatch)")
     with B.batch_invariant():
         y_mma = B.mlx_affine_qmv(x, *weight)
-    assert_within(y_mma, A.qmm(f32(x), *weight_np, weights="bf16"), what="config 0 (tcgen05)")
+    assert_within(y_mma, A.qmm(f32(x), *weight_np, weights="bf16"), what="1536 -> 8960 projection (tcgen05)")
     # Second checker: the C port (fp32 accumulate).
     from oracle import cport
 
     y_c = A.bf16_from_bits(cport.qmm(synth.to_numpy_bits(x), weight_np[0], A.bf16_to_bits(weight_np[1]),
                                      A.bf16_to_bits(weight_np[2])))
-    assert_within(y, y_c, what="config 0 vs C port")
+    assert_within(y, y_c, what="1536 -> 8960 projection vs C port")
 
 
 @pytest.mark.parametrize("rows", [1, 2, 4, 8, 16, 32, 128])
 def test_config1_fused_mlp_llama_1b(cuda_device, rows):
-    """BASELINE config 1: hidden 2048, intermediate 8192, full sizes, through mt_affine_mlp."""
+    """The Llama-3.2-1B MLP: hidden 2048, intermediate 8192, full sizes, through mt_affine_mlp."""
     hidden, inter = 2048, 8192
     gate, up, down = synth.mlp_weights(100, hidden, inter, cuda_device)
     x = synth.activations(5, rows, hidden, cuda_device)
@@ -197,7 +197,7 @@ def test_config1_fused_mlp_llama_1b(cuda_device, rows):
     bits = [(t[0].cpu().numpy(), synth.to_numpy_bits(t[1]), synth.to_numpy_bits(t[2])) for t in (gate, up, down)]
     y_c = A.bf16_from_bits(cport.mlp(synth.to_numpy_bits(x), *bits, synth.to_numpy_bits(res)))
     # Two fp32-accumulating implementations with a bf16 hidden layer in between: 4e-3 of the peak.
-    assert_within(y, y_c, rel=4e-3, what=f"MLP M={rows} vs C port")
+    assert_within(y, y_c, rel=3e-3, what=f"MLP M={rows} vs C port")
     assert A.affine_swiglu_compatible(f32(y), y_c)
     # Linearity in the residual: mlp(x, r) - mlp(x, 0) == r up to the two bf16 stores.
     y0 = execute(x, torch.zeros_like(res))
@@ -223,20 +223,21 @@ def test_single_launch_mlp_up_to_four_rows(cuda_device, hidden, inter):
         for rows in (1, 2, 3):
             assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], f"{rows} rows alone vs in a batch of 4")
         assert_bit_equal(execute(x[3:4], res[3:4]), full[3:4], "last row alone")
-    assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=4e-3, what=f"single-launch MLP {hidden}x{inter}")
+    assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=3e-3, what=f"single-launch MLP {hidden}x{inter}")
     for other in again:
         assert_bit_equal(other, full, "repeat launch")
     assert library.mt_affine_mlp_launches(1, hidden, inter, 0) == 1
     assert_bit_equal(execute(x[:1], res[:1]), full[:1], "default dispatch at one row is this kernel")
     assert library.mt_affine_mlp_launches(4, hidden, inter, _lib.FLAG_MLP_FUSED) == 1
-    # Without a residual, and against the two-kernel path (different fp32 order, same tolerance).
+    # Without a residual, and against the two-kernel path: two approximations of the same MLP (exact
+    # weights here, bf16-rounded weights there), each within 3e-3 of the oracle, so within 6e-3 of each other.
     no_residual = B.mlx_affine_mlp_executor(x, *gate, *up, *down, None)
     with B.force_kernel("mlp_fused"):
         y_plain = no_residual(x, None)
-    assert_within(y_plain, A.mlp(f32(x), *triples_np, None), rel=4e-3, what="single-launch MLP, no residual")
+    assert_within(y_plain, A.mlp(f32(x), *triples_np, None), rel=3e-3, what="single-launch MLP, no residual")
     with B.force_kernel("umma"):
         y_two = execute(x, res)
-    assert_within(full, f32(y_two), rel=4e-3, what="single-launch vs two-kernel path")
+    assert_within(full, f32(y_two), rel=6e-3, what="single-launch vs two-kernel path")
 
 
 @pytest.mark.parametrize("hidden,inter", [(2048, 8192), (1024, 2048), (1024, 1024), (2048, 4096), (512, 1536)])
@@ -256,8 +257,8 @@ def test_single_launch_mlp_on_warp_mma_up_to_eight_rows(cuda_device, hidden, int
             assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], f"{rows} rows alone vs in a batch of 8")
         assert_bit_equal(execute(x[7:8], res[7:8]), full[7:8], "last row alone")
         y_plain = B.mlx_affine_mlp_executor(x, *gate, *up, *down, None)(x, None)
-    assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=4e-3, what=f"warp-MMA MLP {hidden}x{inter}")
-    assert_within(y_plain, A.mlp(f32(x), *triples_np, None), rel=4e-3, what="warp-MMA MLP, no residual")
+    assert_within(full, A.mlp(f32(x), *triples_np, f32(res)), rel=3e-3, what=f"warp-MMA MLP {hidden}x{inter}")
+    assert_within(y_plain, A.mlp(f32(x), *triples_np, None), rel=3e-3, what="warp-MMA MLP, no residual")
     for rows in (2, 3, 4, 8):
         assert library.mt_affine_mlp_launches(rows, hidden, inter, 0) == 1
         assert_bit_equal(execute(x[:rows], res[:rows]), full[:rows], "default dispatch is the warp-MMA kernel")
@@ -283,7 +284,7 @@ def test_single_launch_mlp_refuses_what_it_does_not_serve(cuda_device):
         with pytest.raises(ValueError):
             execute(x, x)  # width that is not a whole number of 1024-column sets
     assert _lib.load().mt_affine_mlp_launches(1, 1536, 1024, 0) == 2
-    assert_within(execute(x, x), A.mlp(f32(x), *[triple_np(t) for t in (gate, up, down)], f32(x)), rel=4e-3)
+    assert_within(execute(x, x), A.mlp(f32(x), *[triple_np(t) for t in (gate, up, down)], f32(x)), rel=3e-3)
 
 
 # ----------------------------------------------------------------------------- batch invariance
@@ -372,7 +373,7 @@ def test_norm_edge_cases(cuda_device):
 
 @pytest.mark.parametrize("k,n", [(256, 128), (256, 256), (1536, 8960)])
 def test_dense_rows_bit_exact_and_batch_invariant(cuda_device, k, n):
-    """BASELINE config 2: dense bf16 small-batch projection, per-row outputs bit-identical."""
+    """Dense bf16 small-batch projection (K=1536, N=8960): per-row outputs bit-identical."""
     w = synth.dense_weight(5, n, k, cuda_device)
     g = synth.dense_weight(6, n, k, cuda_device)
     x = synth.activations(7, 128, k, cuda_device)

@@ -44,7 +44,7 @@ def _run_pair(lib, device, rows, hidden, inter, seed):
     assert_bit_equal(out, reference, f"static vs workspace MLP, rows={rows}")
     oracle = A.mlp(f32(x), triple_np(gate), triple_np(up), triple_np(down), f32(res),
                    weights="exact" if rows <= 8 and lib.mt_affine_mlp_launches(rows, hidden, inter, 0) == 1 else "bf16")
-    assert_within(out, oracle, rel=4e-3, what=f"static MLP vs oracle, rows={rows}")
+    assert_within(out, oracle, rel=3e-3, what=f"static MLP vs oracle, rows={rows}")
 
 
 def test_static_scratch_mlp_matches_workspace_mlp_twice(cuda_device):
