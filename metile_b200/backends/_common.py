@@ -25,6 +25,9 @@ def launch(function, device, *arguments):
     The library takes its SM count, its per-device caches and its launches from the CURRENT device,
     so the tensors' device is made current around the call; a model on cuda:1 works while cuda:0 is
     current."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if torch.cuda.current_device() == index:  # the common case: no device switch to pay for
+        return function(*arguments, stream_pointer(device))
     with torch.cuda.device(device):
         return function(*arguments, stream_pointer(device))
 

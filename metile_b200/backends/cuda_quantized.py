@@ -289,6 +289,10 @@ def mlx_affine_mlp_host_executor(max_rows, hidden_features, gate_weight, gate_sc
     stage_pointers = [ctypes.c_void_p(staging[i].data_ptr()) for i in range(3)]
     row_bytes = hidden_features * 2
 
+    stage_base = staging[0].data_ptr()
+    workspace_pointer, workspace_bytes = pointer(workspace), workspace.numel() * 2
+    entry = lib.mt_affine_mlp_host
+
     def execute(values, residual, out):
         for tensor in (values, residual, out):
             if tensor is None:
@@ -302,15 +306,16 @@ def mlx_affine_mlp_host_executor(max_rows, hidden_features, gate_weight, gate_sc
             raise ValueError(f"host executor was sized for {max_rows} rows, got {rows}")
         # The residual staging area starts right after the rows in use, so that a residual that
         # follows the activations in host memory travels in the same copy.
-        residual_stage = ctypes.c_void_p(staging[0].data_ptr() + rows * row_bytes) if rows < max_rows \
-            else stage_pointers[1]
+        residual_stage = ctypes.c_void_p(stage_base + rows * row_bytes) if rows < max_rows else stage_pointers[1]
         flags = _flags()
-        if (residual is not None and residual.data_ptr() == values.data_ptr() + rows * row_bytes
+        values_address = values.data_ptr()
+        residual_address = None if residual is None else residual.data_ptr()
+        if (residual_address is not None and residual_address == values_address + rows * row_bytes
                 and residual.untyped_storage().data_ptr() == values.untyped_storage().data_ptr()):
             flags |= _lib.FLAG_HOST_PAIR  # two views of one page-locked buffer: one copy moves both
-        code = launch(lib.mt_affine_mlp_host, device, pointer(values), pointer(residual), pointer(out),
-                      stage_pointers[0], residual_stage, stage_pointers[2], *pointers, pointer(workspace),
-                      workspace.numel() * 2, rows, hidden_features, intermediate, group_size, bits, flags)
+        code = launch(entry, device, values_address, residual_address, out.data_ptr(), stage_pointers[0], residual_stage,
+                      stage_pointers[2], *pointers, workspace_pointer, workspace_bytes, rows, hidden_features,
+                      intermediate, group_size, bits, flags)
         _lib.check(code, name)
         return out
 

@@ -557,7 +557,29 @@ inline EncodeTiledFn encode_tiled_fn() {
 // 128-byte swizzle so that a thread reading "its" row's 32 bytes hits distinct banks.
 // Activations as a 2-D bf16 tensor [M, K]; box = 64 columns (128 B, one k-block) x the padded row
 // count, 128-byte swizzle: the box is the B tile of one k-block, rows past M read as zero.
-inline bool encode_activation_map(CUtensorMap* map, const void* base, int M, int K, int box_rows) {
+// A tensor map is a pure function of (address, extents, box): encoding one costs a microsecond or
+// two of host time and a two-kernel MLP needs five, so each host thread remembers the last few it built
+// (weights never move, executors reuse their activation buffers).  Direct-mapped, 64 entries.
+struct TensorMapKey {
+    const void* base;
+    int a, b, box_rows, kind;
+    bool operator==(const TensorMapKey& o) const {
+        return base == o.base && a == o.a && b == o.b && box_rows == o.box_rows && kind == o.kind;
+    }
+};
+struct TensorMapSlot {
+    TensorMapKey key;
+    CUtensorMap map;
+    bool valid;
+};
+inline TensorMapSlot& tensor_map_slot(const TensorMapKey& key) {
+    thread_local TensorMapSlot slots[64] = {};
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(key.base) >> 8;
+    const size_t index = (size_t)((bits ^ (bits >> 7) ^ (uintptr_t)(key.a * 31 + key.b * 7 + key.box_rows + key.kind * 13)) & 63u);
+    return slots[index];
+}
+
+inline bool encode_activation_map_uncached(CUtensorMap* map, const void* base, int M, int K, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
@@ -569,7 +591,7 @@ inline bool encode_activation_map(CUtensorMap* map, const void* base, int M, int
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-inline bool encode_weight_map(CUtensorMap* map, const void* base, int K, int N, int box_rows = kUmmaTileRows) {
+inline bool encode_weight_map_uncached(CUtensorMap* map, const void* base, int K, int N, int box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K / 8, (cuuint64_t)N};
@@ -579,6 +601,36 @@ inline bool encode_weight_map(CUtensorMap* map, const void* base, int K, int N, 
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline bool encode_activation_map(CUtensorMap* map, const void* base, int M, int K, int box_rows) {
+    const TensorMapKey key{base, M, K, box_rows, 1};
+    TensorMapSlot& slot = tensor_map_slot(key);
+    if (!(slot.valid && slot.key == key)) {
+        if (!encode_activation_map_uncached(&slot.map, base, M, K, box_rows)) {
+            slot.valid = false;
+            return false;
+        }
+        slot.key = key;
+        slot.valid = true;
+    }
+    *map = slot.map;
+    return true;
+}
+
+inline bool encode_weight_map(CUtensorMap* map, const void* base, int K, int N, int box_rows = kUmmaTileRows) {
+    const TensorMapKey key{base, K, N, box_rows, 2};
+    TensorMapSlot& slot = tensor_map_slot(key);
+    if (!(slot.valid && slot.key == key)) {
+        if (!encode_weight_map_uncached(&slot.map, base, K, N, box_rows)) {
+            slot.valid = false;
+            return false;
+        }
+        slot.key = key;
+        slot.valid = true;
+    }
+    *map = slot.map;
+    return true;
 }
 
 template <int kT, int kMPad, bool kSwiglu>

@@ -72,6 +72,7 @@ def test_every_call_runs_with_the_tensors_device_current(monkeypatch):
         events.append(("exit", device))
 
     monkeypatch.setattr(torch.cuda, "device", fake_device)
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
     monkeypatch.setattr(_common, "stream_pointer", lambda device: ("stream-of", device))
 
     def entry_point(*arguments):
@@ -81,3 +82,8 @@ def test_every_call_runs_with_the_tensors_device_current(monkeypatch):
     device = torch.device("cuda", 1)
     assert _common.launch(entry_point, device, 1, 2, 3) == 0
     assert events == [("enter", device), ("call", (1, 2, 3, ("stream-of", device))), ("exit", device)]
+    # Already current: no switch, same stream argument.
+    events.clear()
+    here = torch.device("cuda", 0)
+    assert _common.launch(entry_point, here, 4) == 0
+    assert events == [("call", (4, ("stream-of", here)))]
