@@ -1,8 +1,10 @@
 /*
  * C ABI of libmetile_b200.so: the MLX-format affine INT4 projection path for NVIDIA B200
  * (sm_100a).  Plain pointers and sizes only; every pointer is DEVICE memory owned by the
- * caller; the library allocates no device memory, keeps no caller pointer after a call returns, and
- * every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream).
+ * caller (the *_host arguments of mt_affine_mlp_host excepted); the library allocates no device
+ * memory (mt_peer_group_create excepted: the receive buffer of the tensor-parallel sum), keeps no
+ * caller pointer after a call returns, and every call is asynchronous on `stream` (a cudaStream_t
+ * passed as void*; NULL = default stream).
  * Every pointer and the stream must belong to the CURRENT device: the library takes its SM count, its
  * per-device caches and its launches from it.  What the library does hold on each device is a few
  * hundred bytes of status words and barrier counters, and the 4 MiB array of mt_affine_mlp_static.
@@ -111,7 +113,10 @@ int mt_affine_mlp(const void* x, const uint32_t* gate_w, const void* gate_scales
  * x (and of residual, unless residual_host is NULL) from the host buffers into the caller's device
  * staging buffers, mt_affine_mlp on those, and the copy of the result into out_host.  The host
  * buffers should be page-locked (cudaHostAlloc / cudaHostRegister) so the copies are asynchronous;
- * out_host is valid once the stream has been synchronised.  Staging buffers hold M*H bf16 each and
+ * out_host is valid once the stream has been synchronised.  Page-locked, mapped buffers of up to
+ * 512 KB per copy are read and written by small kernels chained to the MLP kernels (a copy engine's
+ * turn between two kernels costs more than such a copy); pageable memory and larger copies go
+ * through cudaMemcpyAsync -- the library asks the runtime what kind of memory each host pointer is.  Staging buffers hold M*H bf16 each and
  * `workspace` is as for mt_affine_mlp; nothing is allocated here.  With MT_FLAG_HOST_PAIR the caller
  * states that residual_host directly follows x_host inside ONE host allocation; if residual_device
  * also directly follows x_device, one copy moves both (small copies cost their latency, not their
