@@ -99,3 +99,35 @@ def test_wrong_format_is_refused(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(config))
     with pytest.raises(ValueError, match="4-bit"):
         checkpoint.load_torch_lm(tmp_path, device="cpu")
+
+
+def test_projection_biases_and_dense_embedding_round_trip(tmp_path):
+    """A Qwen2-style model (additive q / k / v biases) with a dense embedding and its own lm_head."""
+    model = blocks.random_model(seed=7, device="cpu", layers=1)
+    attention = model.layers[0].self_attn
+    for index, name in enumerate(("q_proj", "k_proj", "v_proj")):
+        linear = getattr(attention, name)
+        linear.bias = synth.activations(40 + index, 1, linear.out_features).reshape(-1)
+    config = checkpoint.save_torch_lm(model, tmp_path)
+    assert config["model_type"] == "qwen2" and config["tie_word_embeddings"] is False
+    names = checkpoint.read_checkpoint_tensors(tmp_path)
+    assert "model.layers.0.self_attn.k_proj.bias" in names and "model.embed_tokens.scales" not in names
+    loaded = checkpoint.load_torch_lm(tmp_path, device="cpu")
+    _same(loaded.layers[0].self_attn.v_proj.bias, attention.v_proj.bias)
+    _same(loaded.embed_tokens.weight, model.embed_tokens.weight)
+    assert loaded.layers[0].self_attn.o_proj.bias is None
+
+
+def test_tied_embeddings_need_a_quantised_embedding(tmp_path):
+    model = blocks.random_model(seed=8, device="cpu", layers=1)
+    checkpoint.save_torch_lm(model, tmp_path)
+    config = json.loads((tmp_path / "config.json").read_text())
+    config["tie_word_embeddings"] = True
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    tensors = checkpoint.read_safetensors(tmp_path / "model.safetensors")
+    tensors.pop("__metadata__", None)
+    for name in [n for n in tensors if n.startswith("lm_head.")]:
+        del tensors[name]
+    checkpoint.write_safetensors(tmp_path / "model.safetensors", tensors)
+    with pytest.raises(ValueError, match="tied word embeddings"):
+        checkpoint.load_torch_lm(tmp_path, device="cpu")
