@@ -147,7 +147,14 @@ class KVCache:
         return self.keys[:, :, :self.length], self.values[:, :, :self.length]
 
     def advance(self, steps=1):
+        # The device-side count is incremented, not overwritten with the host's number, so that a
+        # captured CUDA graph of a decode step advances it on every replay.
         self.length += steps
+        self.positions.add_(steps)
+
+    def reset(self, length=0):
+        """Forget everything after the first `length` tokens (host and device counts together)."""
+        self.length = int(length)
         self.positions.fill_(self.length)
 
 

@@ -221,8 +221,11 @@ def execute_attention_decode(module, values, cache, residual=None):
     rotated = backends.rope_kv_append(q, k, v, cache.positions, cache.keys, cache.values, theta=module.rope_theta)
     cache.advance(1)
     scale = getattr(module, "scale", dim ** -0.5)
-    attended = backends.mlx_attention_decode(rotated.view(batch, heads, 1, dim), cache.keys[:, :, :cache.length],
-                                             cache.values[:, :, :cache.length], scale=scale)
+    # The whole cache with the per-sequence lengths on the device (not a slice cut at the host's count):
+    # the same 128-token splits are merged either way, and nothing of the step depends on a host number,
+    # so a captured CUDA graph of it stays valid as the sequences grow.
+    attended = backends.mlx_attention_decode(rotated.view(batch, heads, 1, dim), cache.keys, cache.values,
+                                             scale=scale, lengths=cache.positions)
     attended = attended.view(batch, heads * dim)
     o = module.o_proj
     if residual is None:

@@ -126,3 +126,25 @@ def test_output_projection_at_vocabulary_size(cuda_device, rows):
     packed, scales, biases = weight[0].cpu().numpy(), synth.to_numpy_bits(weight[1]), synth.to_numpy_bits(weight[2])
     reference = A.bf16_from_bits(cport.qmm(synth.to_numpy_bits(x), packed, scales, biases))
     assert_within(y, reference, what=f"lm_head {rows} rows")
+
+
+def test_graphed_decoder_reproduces_the_eager_patched_decode(cuda_device):
+    """One captured decode step replayed per token gives the tokens and the logits of the eager
+    patched loop, bit for bit, and a second prompt through the same graph works as well."""
+    from metile_b200.integrations.graphed import GraphedDecoder
+
+    model, steps = make_model(cuda_device), 10
+    with torch_lm.apply_metile_to_torch_lm(model, **FEATURE_SETS["everything"]) as patch:
+        decoder = GraphedDecoder(model, batch=2, capacity=64)
+        for seed in (5, 6):
+            generator = torch.Generator().manual_seed(seed)
+            tokens = torch.randint(1, 4096, (2, 12), generator=generator).to(cuda_device)
+            eager_tokens, eager_logits, _ = autotune.greedy_decode(model, tokens, steps)
+            first = decoder.prefill(tokens).argmax(dim=-1)
+            generated = decoder.generate(first, steps)
+            torch.cuda.synchronize()
+            assert generated.t().tolist() == eager_tokens, f"prompt {seed}: tokens differ"
+            assert torch.equal(decoder.logits, eager_logits[-1]), f"prompt {seed}: last logits differ"
+            assert decoder.cache[0].length == 12 + steps
+            assert decoder.cache[0].positions.tolist() == [12 + steps] * 2
+        assert not patch.refusals, patch.refusals
