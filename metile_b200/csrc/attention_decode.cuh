@@ -96,6 +96,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_decode_split_kernel(co
     const size_t cache_row0 = ((size_t)bh * p.capacity) * kD;
     const int split_first = split * kAttnSplitTokens;
     const int rows = min(kAttnSplitTokens, n - split_first);  // tokens of this split in use (<= 0: none)
+    // A split past the sequence's end has nothing to do and the merge never reads its partial (callers
+    // pass whole caches with the lengths on the device, so most splits of a short sequence are such).
+    if (rows <= 0 && p.splits > 1) return;
 
     // Both tiles are requested at once, 16 bytes per copy: every byte this CTA will read is in flight
     // before any arithmetic starts.  Two groups, so the score phase can begin when the keys are in.
