@@ -55,6 +55,41 @@ def _child(rank, world, port, case, results):
             assert ok, words
             exchange.close()
             results[rank] = checked
+        elif case == "graph":
+            # The call number lives on the device, so a captured graph of several calls can be replayed.
+            hidden, rows = 2048, 16
+            exchange = tp.PeerAllReduce(device, rank, world, rows * hidden)
+            partials = [synth.activations(500 + 10 * i + rank, rows, hidden, device) for i in range(4)]
+            expected = []
+            for partial in partials:
+                gathered = [torch.empty_like(partial) for _ in range(world)]
+                dist.all_gather(gathered, partial)
+                total = gathered[0].float()
+                for other in gathered[1:]:
+                    total = total + other.float()
+                expected.append(total.to(torch.bfloat16))
+            buffers = [torch.empty_like(partial) for partial in partials]
+            stream = torch.cuda.Stream(device)
+            exchange(partials[0].clone())            # first call outside the graph (lazy set-up)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                with torch.cuda.graph(graph, stream=stream):
+                    for buffer, partial in zip(buffers, partials):
+                        buffer.copy_(partial)
+                        exchange(buffer)
+            torch.cuda.synchronize()
+            for replay in range(5):
+                with torch.cuda.stream(stream):
+                    graph.replay()
+                torch.cuda.synchronize()
+                for index, (buffer, want) in enumerate(zip(buffers, expected)):
+                    assert torch.equal(buffer.view(torch.int16), want.view(torch.int16)), (replay, index)
+            ok, words = _lib.device_status()
+            assert ok, words
+            exchange.close()
+            results[rank] = True
         elif case == "mlp":
             hidden, inter = 1024, 4096
             gate, up, down = synth.mlp_weights(77, hidden, inter)
@@ -141,4 +176,9 @@ def test_sharded_mlp_matches_unsharded_and_is_identical_on_both_ranks():
 
 def test_late_peer_makes_the_wait_run_out_and_the_next_call_recovers():
     results = _run("late")
+    assert results == {0: True, 1: True}
+
+
+def test_exchange_inside_a_replayed_cuda_graph():
+    results = _run("graph")
     assert results == {0: True, 1: True}
