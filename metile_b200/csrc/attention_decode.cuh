@@ -57,39 +57,63 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 constexpr int kAttnThreads = 256;
-constexpr int kAttnKeyPad = 8;  // bf16 elements: a key row in shared memory is 16 bytes longer than in the cache
+constexpr int kAttnRowPad = 8;  // bf16 elements: a tile row in shared memory is 16 bytes longer than in the cache
 
 template <int kD>
 constexpr int attention_smem_bytes() {
-    return kAttnSplitTokens * (kD + kAttnKeyPad) * 2 + kAttnSplitTokens * kD * 2;
+    return 2 * kAttnSplitTokens * (kD + kAttnRowPad) * 2;  // key tile + value tile
 }
 
-// Eight warps: warp w works on tokens [32 (w % 4), +32) of the split and on the query heads of half
-// w / 4 of the group (the first (G+1)/2 heads or the rest), so a tile in shared memory is read by two
-// warps and the FMAs of a token are shared between them.
+// Four 8x8 b16 matrices from shared memory into the fragment layout of mma.sync (lane l supplies the
+// address of row l % 8 of matrix l / 8); `trans` delivers each matrix transposed.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(ptx::smem_u32(row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(ptx::smem_u32(row)));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], const void* row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1]) : "r"(ptx::smem_u32(row)));
+}
+// D += A (16x16, row) * B (16x8, col), bf16 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The arithmetic runs on the tensor cores (mma.sync m16n8k16, bf16 x bf16 -> fp32):
+//   scores : S[16 tokens x 8 heads] = K[16 x D] . Q^T[D x 8]  -- the query-head group of a KV head (up to 8
+//            heads) is the N dimension; warp w owns tokens [16 w, 16 w + 16); keys and queries enter as the
+//            bf16 numbers they are and the scale multiplies the fp32 sums;
+//   softmax: one warp per head over the split's 128 scores (shared memory), fp32; the probabilities are
+//            written as TWO bf16 numbers hi + lo (relative error 2^-17), so that the second product runs
+//            on the tensor cores without giving up the fp32 probabilities of the reference;
+//   values : O[8 heads x D] = P[8 x 128 tokens] . V[128 x D]  -- warp w owns D / 8 head-dim columns, the value
+//            tile is read with transposing matrix loads, hi and lo are two MMAs into one accumulator.
+// Measured against the CUDA-core form of the same kernel (one token per lane, FMAs against the queries in
+// shared memory), which spent two thirds of its instructions on converts and shared-memory reads.
 template <int kD, int kG>
 __global__ void __launch_bounds__(kAttnThreads) attention_decode_split_kernel(const AttentionParams p) {
-    constexpr int kPerLane = kD / 32;  // head-dim elements a lane owns in the value phase (2 or 4)
-    constexpr int kGPad = 8;
-    constexpr int kFirstHalf = (kG + 1) / 2;
-    constexpr int kKeyRow = kD + kAttnKeyPad;  // elements; 16 bytes of padding make lane-per-token reads conflict-free
+    constexpr int kRow = kD + kAttnRowPad;   // elements; the 16 bytes of padding keep matrix loads conflict-free
+    constexpr int kSlices = kD / 16;         // k-steps of the score product
+    constexpr int kColsPerWarp = kD / 8;     // head-dim columns a warp owns in the value product (16 or 8)
+    constexpr int kNTiles = kColsPerWarp / 8;
+    constexpr int kProbRow = kAttnSplitTokens + 8;
     extern __shared__ __align__(16) uint16_t tiles[];
-    uint16_t* key_tile = tiles;                               // [128][kD + 8]
-    uint16_t* value_tile = tiles + kAttnSplitTokens * kKeyRow;  // [128][kD]
-    __shared__ __align__(16) float q_shared[kG][kD];
-    __shared__ __align__(16) float prob[4][32][kGPad];
-    __shared__ float warp_max[4][kG], warp_sum[4][kG];
-    // The four token groups' outputs reuse the key tile once every warp is done with it.
-    float* warp_out = reinterpret_cast<float*>(key_tile);     // [4][kG][kD]
-    static_assert(4 * kG * kD * 4 <= kAttnSplitTokens * kKeyRow * 2, "warp outputs fit the key tile");
+    uint16_t* key_tile = tiles;                                // [128][kRow]
+    uint16_t* value_tile = tiles + kAttnSplitTokens * kRow;    // [128][kRow]
+    __shared__ __align__(16) uint16_t prob_hi[8][kProbRow], prob_lo[8][kProbRow];
+    __shared__ float warp_max[8][8], warp_sum[8][8];           // [warp][head]
 
     const int split = blockIdx.x;
     const int bh = blockIdx.y;                     // b * Hkv + h
     const int b = bh / p.kv_heads, h = bh - b * p.kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int group = warp & 3, half = warp >> 2;
-    const int g_begin = half == 0 ? 0 : kFirstHalf;
-    const int g_end = half == 0 ? kFirstHalf : kG;
+    const int g = lane >> 2, t = lane & 3;         // fragment coordinates
     ptx::griddep_launch_dependents();
     ptx::griddep_wait();                           // q and the newest cache row are the preceding kernels' output
     const int n = p.lengths ? p.lengths[b] : p.tokens;
@@ -105,133 +129,161 @@ __global__ void __launch_bounds__(kAttnThreads) attention_decode_split_kernel(co
     constexpr int kChunks = kD / 8;
     for (int c = threadIdx.x; c < rows * kChunks; c += kAttnThreads) {
         const int row = c / kChunks, chunk = c - row * kChunks;
-        cp_async_16(key_tile + row * kKeyRow + chunk * 8, p.k + cache_row0 + (size_t)(split_first + row) * kD + chunk * 8);
+        cp_async_16(key_tile + row * kRow + chunk * 8, p.k + cache_row0 + (size_t)(split_first + row) * kD + chunk * 8);
     }
     cp_async_commit();
     for (int c = threadIdx.x; c < rows * kChunks; c += kAttnThreads) {
         const int row = c / kChunks, chunk = c - row * kChunks;
-        cp_async_16(value_tile + row * kD + chunk * 8, p.v + cache_row0 + (size_t)(split_first + row) * kD + chunk * 8);
+        cp_async_16(value_tile + row * kRow + chunk * 8, p.v + cache_row0 + (size_t)(split_first + row) * kD + chunk * 8);
     }
     cp_async_commit();
+    // Rows past the sequence's end enter the value product with probability zero; their bytes must
+    // still be numbers (0 x NaN is NaN).  Key rows past the end only produce scores that are masked.
+    const int first_unused = max(rows, 0);
+    for (int c = threadIdx.x; c < (kAttnSplitTokens - first_unused) * kChunks; c += kAttnThreads) {
+        const int row = first_unused + c / kChunks, chunk = c % kChunks;
+        *reinterpret_cast<uint4*>(value_tile + row * kRow + chunk * 8) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(key_tile + row * kRow + chunk * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
 
-    // Scaled queries of this KV head's group, fp32 (the cast comes before the scale multiplies).
-    for (int idx = threadIdx.x; idx < kG * kD; idx += kAttnThreads) {
-        const int g = idx / kD, d = idx - g * kD;
-        const size_t at = ((size_t)b * p.q_heads + (size_t)h * kG + g) * kD + d;
-        q_shared[g][d] = bf16_bits_to_f32(ptx::ld_global_dependent_u16(p.q + at)) * p.scale;
+    // Query fragments (the B operand of the score product): head g, dims 16 s + 2 t (+1) and + 8.
+    uint32_t qf[kSlices][2];
+    {
+        const uint16_t* qrow = p.q + ((size_t)b * p.q_heads + (size_t)h * kG + min(g, kG - 1)) * kD;
+#pragma unroll
+        for (int s = 0; s < kSlices; ++s) {
+            uint32_t lo, hi;
+            asm volatile("ld.global.u32 %0, [%1];" : "=r"(lo) : "l"(qrow + 16 * s + 2 * t));
+            asm volatile("ld.global.u32 %0, [%1];" : "=r"(hi) : "l"(qrow + 16 * s + 2 * t + 8));
+            qf[s][0] = g < kG ? lo : 0u;
+            qf[s][1] = g < kG ? hi : 0u;
+        }
     }
     cp_async_wait<1>();
     __syncthreads();
 
-    const int local = group * 32 + lane;           // this lane's token inside the split
-    const bool valid = local < rows;
-    const int first = group * 32;
-    const int count = min(32, rows - first);       // tokens of this warp in use (<= 0: none)
-
-    // ---------------------------------------------------------------- scores: one token per lane
-    float score[kFirstHalf];
+    // ---------------------------------------------------------------- scores: 16 tokens per warp
+    // c0, c1: token 16 w + g, heads 2 t and 2 t + 1; c2, c3: token 16 w + g + 8.  The scores stay in
+    // these registers through the softmax; only the per-warp maxima and sums meet in shared memory.
+    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    {
+        const uint16_t* a_row = key_tile + (16 * warp + (lane & 15)) * kRow + 8 * (lane >> 4);
 #pragma unroll
-    for (int j = 0; j < kFirstHalf; ++j) score[j] = 0.0f;
-    if (valid) {
-        const uint16_t* key = key_tile + local * kKeyRow;
-#pragma unroll 4
-        for (int d0 = 0; d0 < kD; d0 += 8) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(key + d0);
-            const float kf[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
-                                 bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
-#pragma unroll
-            for (int j = 0; j < kFirstHalf; ++j) {
-                const int g = g_begin + j;
-                if (g >= g_end) break;
-                const float4 qa = *reinterpret_cast<const float4*>(&q_shared[g][d0]);
-                const float4 qb = *reinterpret_cast<const float4*>(&q_shared[g][d0 + 4]);
-                float s = score[j];
-                s = fmaf(qa.x, kf[0], s); s = fmaf(qa.y, kf[1], s); s = fmaf(qa.z, kf[2], s); s = fmaf(qa.w, kf[3], s);
-                s = fmaf(qb.x, kf[4], s); s = fmaf(qb.y, kf[5], s); s = fmaf(qb.z, kf[6], s); s = fmaf(qb.w, kf[7], s);
-                score[j] = s;
-            }
+        for (int s = 0; s < kSlices; ++s) {
+            uint32_t a[4];
+            ldmatrix_x4(a, a_row + 16 * s);
+            mma_bf16_16816(c, a, qf[s][0], qf[s][1]);
         }
     }
-    // ---------------------------------------------------------------- softmax over the warp's tokens
-    float block_max[kFirstHalf], block_sum[kFirstHalf];
+    const int token0 = 16 * warp + g, token1 = token0 + 8;
+    c[0] = token0 < rows ? c[0] * p.scale : -INFINITY;
+    c[1] = token0 < rows ? c[1] * p.scale : -INFINITY;
+    c[2] = token1 < rows ? c[2] * p.scale : -INFINITY;
+    c[3] = token1 < rows ? c[3] * p.scale : -INFINITY;
+    {
+        float even = fmaxf(c[0], c[2]), odd = fmaxf(c[1], c[3]);   // heads 2 t and 2 t + 1 over this lane's tokens
 #pragma unroll
-    for (int j = 0; j < kFirstHalf; ++j) {
-        const int g = g_begin + j;
-        if (g >= g_end) break;
-        float m = valid ? score[j] : -INFINITY;
-#pragma unroll
-        for (int offset = 16; offset >= 1; offset >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, offset));
-        const float e = valid ? __expf(score[j] - m) : 0.0f;
-        prob[group][lane][g] = e;
-        block_max[j] = m;
-        block_sum[j] = warp_sum_xor(e);
-    }
-    cp_async_wait<0>();
-    __syncthreads();  // values have landed; every warp is done with the key tile and has written its probabilities
-    // ---------------------------------------------------------------- values: lanes own head-dim slices
-    float acc[kFirstHalf][kPerLane];
-#pragma unroll
-    for (int j = 0; j < kFirstHalf; ++j)
-#pragma unroll
-        for (int e = 0; e < kPerLane; ++e) acc[j][e] = 0.0f;
-    if (count > 0) {
-        const uint16_t* value = value_tile + first * kD + lane * kPerLane;
-#pragma unroll 4
-        for (int t = 0; t < count; ++t) {
-            float vf[kPerLane];
-            if constexpr (kPerLane == 4) {
-                const uint2 raw = *reinterpret_cast<const uint2*>(value + t * kD);
-                vf[0] = bf16_lo(raw.x); vf[1] = bf16_hi(raw.x); vf[2] = bf16_lo(raw.y); vf[3] = bf16_hi(raw.y);
-            } else {
-                const uint32_t raw = *reinterpret_cast<const uint32_t*>(value + t * kD);
-                vf[0] = bf16_lo(raw); vf[1] = bf16_hi(raw);
-            }
-            const float4 pa = *reinterpret_cast<const float4*>(&prob[group][t][0]);
-            const float4 pb = *reinterpret_cast<const float4*>(&prob[group][t][4]);
-            const float pg[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
-#pragma unroll
-            for (int j = 0; j < kFirstHalf; ++j) {
-                const int g = half == 0 ? j : kFirstHalf + j;   // a compile-time index in each branch of `half`
-                if (g >= g_end) break;
-#pragma unroll
-                for (int e = 0; e < kPerLane; ++e) acc[j][e] = fmaf(half == 0 ? pg[j] : pg[(kFirstHalf + j) & 7], vf[e], acc[j][e]);
-            }
+        for (int offset = 4; offset <= 16; offset <<= 1) {        // over g: the warp's 16 tokens
+            even = fmaxf(even, __shfl_xor_sync(0xFFFFFFFFu, even, offset));
+            odd = fmaxf(odd, __shfl_xor_sync(0xFFFFFFFFu, odd, offset));
         }
-    }
-    // ---------------------------------------------------------------- merge the four token groups, in order
-#pragma unroll
-    for (int j = 0; j < kFirstHalf; ++j) {
-        const int g = g_begin + j;
-        if (g >= g_end) break;
-        if (lane == 0) {
-            warp_max[group][g] = block_max[j];
-            warp_sum[group][g] = block_sum[j];
+        if (g == 0) {
+            warp_max[warp][2 * t] = even;
+            warp_max[warp][2 * t + 1] = odd;
         }
-#pragma unroll
-        for (int e = 0; e < kPerLane; ++e) warp_out[(group * kG + g) * kD + lane * kPerLane + e] = acc[j][e];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < kG * kD; idx += kAttnThreads) {
-        const int g = idx / kD, d = idx - g * kD;
-        float m = warp_max[0][g];
+    // ---------------------------------------------------------------- softmax over the split's 128 tokens
+    {
+        float m_even = warp_max[0][2 * t], m_odd = warp_max[0][2 * t + 1];
 #pragma unroll
-        for (int w = 1; w < 4; ++w) m = fmaxf(m, warp_max[w][g]);
-        float total = 0.0f, value = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float factor = warp_max[w][g] == -INFINITY ? 0.0f : __expf(warp_max[w][g] - m);
-            total = fmaf(warp_sum[w][g], factor, total);
-            value = fmaf(warp_out[(w * kG + g) * kD + d], factor, value);
+        for (int w = 1; w < 8; ++w) {
+            m_even = fmaxf(m_even, warp_max[w][2 * t]);
+            m_odd = fmaxf(m_odd, warp_max[w][2 * t + 1]);
         }
-        if (p.splits == 1) {
-            const size_t at = ((size_t)b * p.q_heads + (size_t)h * kG + g) * kD + d;
-            p.out[at] = f32_to_bf16_bits(value / total);
+        // Masked tokens: exp(-inf - m) = 0; a split with no token at all has m = -inf and contributes 0.
+        const float e0 = m_even == -INFINITY ? 0.0f : __expf(c[0] - m_even);
+        const float e1 = m_odd == -INFINITY ? 0.0f : __expf(c[1] - m_odd);
+        const float e2 = m_even == -INFINITY ? 0.0f : __expf(c[2] - m_even);
+        const float e3 = m_odd == -INFINITY ? 0.0f : __expf(c[3] - m_odd);
+        float even = e0 + e2, odd = e1 + e3;
+#pragma unroll
+        for (int offset = 4; offset <= 16; offset <<= 1) {
+            even += __shfl_xor_sync(0xFFFFFFFFu, even, offset);
+            odd += __shfl_xor_sync(0xFFFFFFFFu, odd, offset);
+        }
+        if (g == 0) {
+            warp_sum[warp][2 * t] = even;
+            warp_sum[warp][2 * t + 1] = odd;
+        }
+        // The probabilities as hi + lo (two bf16 numbers each), [head][token]; heads past the group get
+        // zeros (their queries were zero, so e = exp(0 - 0) = 1 must not reach the padded rows).
+        const float e[4] = {e0, e1, e2, e3};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int head = 2 * t + (i & 1), token = i < 2 ? token0 : token1;
+            const float value = head < kG ? e[i] : 0.0f;
+            const uint16_t hi = f32_to_bf16_bits(value);
+            prob_hi[head][token] = hi;
+            prob_lo[head][token] = f32_to_bf16_bits(value - bf16_bits_to_f32(hi));
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // values have landed and every probability is written
+    // ---------------------------------------------------------------- values: D / 8 columns per warp
+    float acc[kNTiles][4];
+#pragma unroll
+    for (int nt = 0; nt < kNTiles; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.0f;
+    const int dim0 = warp * kColsPerWarp;
+#pragma unroll
+    for (int ks = 0; ks < kAttnSplitTokens / 16; ++ks) {
+        if (16 * ks >= rows) break;  // whole k-steps past the end contribute nothing
+        // A operand: P[head g][tokens 16 ks + 2 t (+1)] and + 8; rows 8..15 of the 16-row tile are zero.
+        uint32_t a_hi[4], a_lo[4];
+        a_hi[0] = *reinterpret_cast<const uint32_t*>(&prob_hi[g][16 * ks + 2 * t]);
+        a_hi[2] = *reinterpret_cast<const uint32_t*>(&prob_hi[g][16 * ks + 2 * t + 8]);
+        a_lo[0] = *reinterpret_cast<const uint32_t*>(&prob_lo[g][16 * ks + 2 * t]);
+        a_lo[2] = *reinterpret_cast<const uint32_t*>(&prob_lo[g][16 * ks + 2 * t + 8]);
+        a_hi[1] = a_hi[3] = a_lo[1] = a_lo[3] = 0u;
+        if constexpr (kNTiles == 2) {
+            uint32_t bfrag[4];
+            ldmatrix_x4_trans(bfrag, value_tile + (16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8) * kRow + dim0 + 8 * (lane >> 4));
+            mma_bf16_16816(acc[0], a_hi, bfrag[0], bfrag[1]);
+            mma_bf16_16816(acc[0], a_lo, bfrag[0], bfrag[1]);
+            mma_bf16_16816(acc[1], a_hi, bfrag[2], bfrag[3]);
+            mma_bf16_16816(acc[1], a_lo, bfrag[2], bfrag[3]);
         } else {
-            float* row = p.partial + (((size_t)bh * p.splits + split) * kG + g) * (kD + 2);
-            row[d] = value;
-            if (d == 0) {
-                row[kD] = m;
-                row[kD + 1] = total;
+            uint32_t bfrag[2];
+            ldmatrix_x2_trans(bfrag, value_tile + (16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8) * kRow + dim0);
+            mma_bf16_16816(acc[0], a_hi, bfrag[0], bfrag[1]);
+            mma_bf16_16816(acc[0], a_lo, bfrag[0], bfrag[1]);
+        }
+    }
+    // acc[nt][0], [1]: head g, dims dim0 + 8 nt + 2 t (+1); [2], [3] belong to the padded heads.
+    if (g < kG) {
+        float m = warp_max[0][g], total = warp_sum[0][g];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) {   // the eight warps' sums in warp order
+            m = fmaxf(m, warp_max[w][g]);
+            total += warp_sum[w][g];
+        }
+#pragma unroll
+        for (int nt = 0; nt < kNTiles; ++nt) {
+            const int d = dim0 + 8 * nt + 2 * t;
+            if (p.splits == 1) {
+                const size_t at = ((size_t)b * p.q_heads + (size_t)h * kG + g) * kD + d;
+                const uint32_t pair = pack_bf16x2(acc[nt][0] / total, acc[nt][1] / total);
+                *reinterpret_cast<uint32_t*>(p.out + at) = pair;
+            } else {
+                float* row = p.partial + (((size_t)bh * p.splits + split) * kG + g) * (kD + 2);
+                row[d] = acc[nt][0];
+                row[d + 1] = acc[nt][1];
+                if (d == 0) {
+                    row[kD] = m;
+                    row[kD + 1] = total;
+                }
             }
         }
     }
