@@ -10,18 +10,14 @@
 // every query head of a KV head, so each cache byte is read once.
 //
 // Split over the KV range ("flash decoding"): CTA (s, b*Hkv + h) takes tokens [128 s, 128 s + 128) of
-// one (sequence, KV head).  Its key and value tiles (32 KB each at head dim 128) are copied to
-// shared memory by 16-byte asynchronous copies issued before anything else, so the whole 64 KB is in
-// flight at once; a warp takes 32 tokens, one token per lane, and half of the group's query heads.
-//   scores : the lane reads ITS token's key row from shared memory (rows padded by 16 bytes: no bank
-//            conflicts) and multiplies it with the scaled query rows, which sit in shared memory as
-//            fp32 (broadcast reads).  No shuffles.
-//   softmax: per query head, maximum and sum over the warp's 32 tokens by butterfly; probabilities
-//            go to shared memory.
-//   values : lanes now own head-dim slices (coalesced 256-byte rows) and accumulate
-//            O[g][d] += p[token][g] * V[token][d] over the warp's tokens.
-//   merge  : the four warps' (max, sum, O) are merged in warp order, the CTA's partial goes to the
-//            caller's scratch, and a second kernel merges the splits in split order.
+// one (sequence, KV head).  Its key and value tiles (35 KB each at head dim 128, rows padded by 16
+// bytes) are copied to shared memory by 16-byte asynchronous copies issued before anything else, so
+// the whole tile pair is in flight at once; the arithmetic runs on the tensor cores (see the kernel):
+// scores K . Q^T with the KV head's query-head group as the N dimension, softmax on the score
+// fragments in registers, values P . V with the probabilities split into two bf16 numbers; the CTA's
+// partial (max, sum, O) goes to the caller's scratch and a second kernel merges the splits in split
+// order.  The reference multiplies fp32 casts of the same bf16 inputs (:58-62); the products are
+// exact either way, the sums are fp32, and the scale multiplies the fp32 score instead of the query.
 // The split size is a constant, so a (sequence, head)'s bits depend on its own KV length only -- not
 // on how many sequences share the launch.
 //
