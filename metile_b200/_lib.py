@@ -48,6 +48,7 @@ SIGNATURES = {
     "mt_rope_kv_append": (_i, [_p, _p, _p, ctypes.c_longlong, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p]),
     "mt_peer_group_create": (_i, [_i, _i, _z, ctypes.POINTER(ctypes.c_void_p), _p]),
     "mt_peer_group_connect": (_i, [_p, _p]),
+    "mt_peer_group_set_mode": (_i, [_p, _i]),
     "mt_peer_all_reduce": (_i, [_p, _p, _p, _z, _u, _p]),
     "mt_peer_group_destroy": (_i, [_p]),
     "mt_dense_rows": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),

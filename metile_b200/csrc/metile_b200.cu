@@ -660,6 +660,13 @@ int mt_peer_all_reduce(void* group_pointer, const void* partial, void* out, size
     return launch_peer_reduce(group, partial, out, elements, 1000000ull * limit_ms, static_cast<cudaStream_t>(stream));
 }
 
+int mt_peer_group_set_mode(void* group_pointer, int mode) {
+    if (!group_pointer) return MT_ERR_NULL;
+    if (mode < 0 || mode > 2) return MT_ERR_SHAPE;
+    static_cast<PeerGroup*>(group_pointer)->mode = mode;
+    return MT_OK;
+}
+
 int mt_peer_group_destroy(void* group_pointer) {
     if (!group_pointer) return MT_OK;
     PeerGroup* group = static_cast<PeerGroup*>(group_pointer);

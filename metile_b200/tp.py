@@ -41,7 +41,9 @@ class PeerAllReduce:
     on one stream (calls of one group must not overlap on a GPU); a CUDA graph containing calls may be
     replayed, the same number of times on every rank."""
 
-    def __init__(self, device, rank, world, max_elements, *, group=None, limit_ms=1000):
+    MODES = {"auto": 0, "one_shot": 1, "two_shot": 2}
+
+    def __init__(self, device, rank, world, max_elements, *, group=None, limit_ms=1000, mode="auto"):
         import torch.distributed as dist
 
         from . import _lib
@@ -63,6 +65,9 @@ class PeerAllReduce:
             gathered[0] = mine.raw
         with torch.cuda.device(self.device):
             _lib.check(self._lib.mt_peer_group_connect(self._handle, b"".join(gathered)), "mt_peer_group_connect")
+        if mode not in self.MODES:
+            raise ValueError('mode must be "auto", "one_shot" or "two_shot"')
+        _lib.check(self._lib.mt_peer_group_set_mode(self._handle, self.MODES[mode]), "mt_peer_group_set_mode")
 
     def __call__(self, tensor):
         if tensor.dtype != torch.bfloat16 or not tensor.is_cuda or tensor.device != self.device:

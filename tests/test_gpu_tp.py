@@ -35,9 +35,10 @@ def _child(rank, world, port, case, results):
     torch.cuda.set_device(device)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
-        if case == "sum":
+        if case in ("sum", "sum_two_shot"):
             hidden = 5120
-            exchange = tp.PeerAllReduce(device, rank, world, 128 * hidden)
+            exchange = tp.PeerAllReduce(device, rank, world, 128 * hidden,
+                                        mode="two_shot" if case == "sum_two_shot" else "auto")
             checked = 0
             for call, rows in enumerate([1, 128, 16, 1, 1, 64, 128, 2] * 4):
                 partial = synth.activations(1000 + 10 * call + rank, rows, hidden, device)
@@ -166,6 +167,13 @@ def _run(case):
 
 def test_peer_sum_equals_the_rank_order_sum_bit_for_bit():
     results = _run("sum")
+    assert results == {0: 32, 1: 32}
+
+
+def test_two_shot_exchange_gives_the_same_bits():
+    """Reduce-scatter then all-gather through peer memory (the form large messages among three or more
+    ranks take), forced here on two ranks: same rank-order sums, bit for bit."""
+    results = _run("sum_two_shot")
     assert results == {0: 32, 1: 32}
 
 
