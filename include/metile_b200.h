@@ -206,9 +206,9 @@ int mt_rope_kv_append(const void* q, const void* k, const void* v, long long row
  * tensor-parallel form of the fused MLP: the down projection of a K-sharded MLP leaves a partial
  * [M, H] result on every rank.  NO COUNTERPART IN THE REFERENCE, which is single-device.
  *
- * One kernel per rank stores the partial into every peer's receive buffer over NVLink (large
- * messages among three or more ranks: only the segment each peer reduces, then the reduced segment
- * to everyone), signals, waits
+ * One kernel per rank stores the partial into every peer's receive buffer over NVLink (very large
+ * messages among many ranks: only the segment each peer reduces, then the reduced segment to
+ * everyone), signals, waits
  * (bounded by limit_ms, 1..2000; on expiry nothing is written to `out` and mt_device_status reports
  * code 0x9E0 with the peer that did not arrive) and adds the partials in rank order in fp32, so every
  * rank obtains the same bits whatever the message size.
@@ -228,9 +228,9 @@ int mt_rope_kv_append(const void* q, const void* k, const void* v, long long row
 int mt_peer_group_create(int rank, int world, size_t slot_bytes, void** group_out,
                          void* ipc_handle_out);
 int mt_peer_group_connect(void* group, const void* ipc_handles);
-/* mode 0 (default): one shot, or two shots (reduce-scatter then all-gather, both by peer stores) from
- * three ranks and half a megabyte of stores on; 1: always one shot; 2: always two shots.  Every rank
- * must choose the same. */
+/* mode 0 (default): one shot, or two shots (reduce-scatter then all-gather, both by peer stores) where
+ * one shot would store more than 4 MB per rank among six or more ranks; 1: always one shot; 2: always
+ * two shots.  Every rank must choose the same. */
 int mt_peer_group_set_mode(void* group, int mode);
 int mt_peer_all_reduce(void* group, const void* partial, void* out, size_t elements,
                        unsigned int limit_ms, void* stream);

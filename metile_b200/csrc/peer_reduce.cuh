@@ -17,7 +17,7 @@
 // advances it, so a launch carries no per-call argument and a captured CUDA graph of it can be
 // replayed (every rank must replay the same number of launches, as it must make the same calls).
 //
-// Large messages among three or more ranks take TWO shots instead (peer_reduce_two_shot_kernel): every
+// Very large messages among many ranks take TWO shots instead (peer_reduce_two_shot_kernel): every
 // rank first sends each peer only the segment that peer will reduce, reduces its own segment in rank
 // order, then sends the reduced segment to everyone -- 2 (world-1)/world messages' worth of stores
 // per rank instead of world-1, for a second round of flags.  Both phases write into the same slots:
@@ -268,12 +268,14 @@ inline int launch_peer_reduce(PeerGroup* group, const void* partial, void* out, 
     p.flags_offset = group->flags_offset;
     p.limit_ns = limit_ns;
     // The grid and the choice between one and two shots depend on the message size and the rank count
-    // only, so every rank launches the same kernel with the same grid.  Two shots pay a second round
-    // of flags to send 2 (world-1)/world messages instead of world-1: from three ranks and half a
-    // megabyte of stores on.
+    // only, so every rank launches the same kernel with the same grid.  Two shots send
+    // 2 (world-1)/world messages instead of world-1 but pay a second round of stores, system fence and
+    // flags (about 10 us): measured on four GPUs at 1.3 MB, 34.7 us against 25.6 us for one shot, so the
+    // default takes two shots only where one shot would store more than 4 MB per rank among six or more
+    // ranks (not measured there: no such machine was to be had).
     const bool two_shot = group->world >= 2 &&
-                          (group->mode == 2 || (group->mode == 0 && group->world >= 3 &&
-                                                elements * 2 * (size_t)(group->world - 1) >= (512u << 10)));
+                          (group->mode == 2 || (group->mode == 0 && group->world >= 6 &&
+                                                elements * 2 * (size_t)(group->world - 1) >= (4u << 20)));
     const unsigned int units = two_shot ? (p.vectors + group->world - 1) / group->world : p.vectors;
     int grid = (int)((units + kPeerThreads - 1) / kPeerThreads);
     grid = grid < 1 ? 1 : grid > kPeerMaxCtas ? kPeerMaxCtas : grid;

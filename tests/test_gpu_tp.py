@@ -171,7 +171,7 @@ def test_peer_sum_equals_the_rank_order_sum_bit_for_bit():
 
 
 def test_two_shot_exchange_gives_the_same_bits():
-    """Reduce-scatter then all-gather through peer memory (the form large messages among three or more
+    """Reduce-scatter then all-gather through peer memory (the form very large messages among many
     ranks take), forced here on two ranks: same rank-order sums, bit for bit."""
     results = _run("sum_two_shot")
     assert results == {0: 32, 1: 32}
