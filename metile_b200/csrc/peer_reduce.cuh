@@ -81,8 +81,11 @@ __device__ __forceinline__ void accumulate_bf16x8(float* acc, const uint4& v) {
 }
 
 // Raises this CTA's flag for `call` on every peer (flag array `which`: 0 = first shot, 1 = second) and
-// waits, bounded, for the peers' flags here.  Called by all threads after their stores and a
-// __threadfence_system(); returns after a __syncthreads() with *gave_up set if a peer never arrived.
+// waits, bounded, for the peers' flags here.  Called by all threads after their stores: the CTA
+// barrier orders those stores before the signalling threads, whose system-scope fence and release
+// store then publish them (one fence per signalling thread instead of one per thread of the CTA: a
+// system fence waits for every store the SM has in flight).  Returns after a __syncthreads() with
+// *gave_up set if a peer never arrived.
 __device__ __forceinline__ void peer_signal_and_wait(unsigned char* const* peers, const PeerReduceParams& p, int which,
                                                      unsigned int call, int* gave_up) {
     __syncthreads();
@@ -90,6 +93,7 @@ __device__ __forceinline__ void peer_signal_and_wait(unsigned char* const* peers
     if (peer < p.world && peer != p.rank) {
         const size_t flags = p.flags_offset + (size_t)which * (kPeerMaxWorld * kPeerMaxCtas + 4) * sizeof(unsigned int);
         unsigned int* theirs = reinterpret_cast<unsigned int*>(peers[peer] + flags) + p.rank * kPeerMaxCtas + blockIdx.x;
+        __threadfence_system();
         st_release_sys(theirs, call);
         const unsigned int* here =
             reinterpret_cast<const unsigned int*>(peers[p.rank] + flags) + peer * kPeerMaxCtas + blockIdx.x;
@@ -175,7 +179,6 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_two_shot_kernel(cons
         uint4* theirs = reinterpret_cast<uint4*>(peers[j] + mine);
         for (unsigned int i = begin + threadIdx.x; i < end; i += blockDim.x) theirs[i] = p.partial[i];
     }
-    __threadfence_system();
     peer_signal_and_wait(peers, p, 0, call, &gave_up);
     if (!gave_up) {
         // this rank's segment: add in rank order, keep the result and send it to everyone
@@ -187,7 +190,6 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_two_shot_kernel(cons
             for (int j = 0; j < p.world; ++j)
                 if (j != p.rank) reinterpret_cast<uint4*>(peers[j] + mine)[i] = r;
         }
-        __threadfence_system();
     }
     peer_signal_and_wait(peers, p, 1, call, &gave_up);
     if (!gave_up) {
@@ -232,7 +234,6 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(const PeerRed
         for (int peer = 0; peer < p.world; ++peer)
             if (peer != p.rank) reinterpret_cast<uint4*>(peers[peer] + mine)[i] = v;
     }
-    __threadfence_system();
     // 2. signal every peer, wait until each peer's CTA of the same index has pushed its part here
     peer_signal_and_wait(peers, p, 0, call, &gave_up);
 
