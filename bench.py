@@ -968,6 +968,8 @@ def run_ours(args):
 
     if rank == 0:
         launches_per_sweep = sum(library.mt_affine_mlp_launches(m, hidden, inter // world, 0) for m in sweep)
+        if tp:
+            launches_per_sweep += len(sweep)  # the exchange kernel after every shard MLP
         line = {
             "metric": "int4_fused_mlp_weight_GBps",
             "value": value,
