@@ -15,7 +15,16 @@ def pointer(tensor):
     return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
 
 
+# torch's own fast path to the raw handle of a device's current stream (what its compiled-kernel
+# launchers use); `torch.cuda.current_stream()` builds a Stream object first and costs about six
+# microseconds per call, a quarter of the host time of one operator call here.
+_raw_current_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_pointer(device):
+    if _raw_current_stream is not None:
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        return ctypes.c_void_p(_raw_current_stream(index))
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
