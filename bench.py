@@ -1012,8 +1012,9 @@ def run_ours(args):
 
 
 def run_capture(spec):
-    """Six launches of one operator at the Llama-3.2-1B shape over six weight sets (170 MB, larger than
-    L2), nothing timed and nothing printed but a status line: the process profilers attach to."""
+    """Six launches of one operator over rotating weight sets larger than L2 (the Llama-3.2-1B MLP and
+    its projections, decode attention, dense bf16 rows, the LM head), nothing timed and nothing printed
+    but a status line: the process profilers attach to."""
     import torch
 
     from metile_b200 import _lib
@@ -1034,6 +1035,26 @@ def run_capture(spec):
                   for i in range(6)]
         for keys, values in caches:
             B.mlx_attention_decode(query, keys, values, scale=dim ** -0.5)
+        torch.cuda.synchronize()
+        ok, words = _lib.device_status()
+        print(json.dumps({"capture": spec, "device_status_ok": bool(ok)}))
+        return 0 if ok else 1
+    if op in ("dense", "lm_head"):
+        # dense: bf16 rows against six 1536 x 8960 matrices (165 MB); lm_head: the INT4 projection onto a
+        # 128256-token vocabulary, two weight sets (148 MB each).
+        if op == "dense":
+            k, n = 1536, 8960
+            weights = [synth.dense_weight(950 + i, n, k, device) for i in range(6)]
+        else:
+            k, n = 2048, 128256
+            weights = [synth.affine_weight(700 + i, n, k, device) for i in range(2)] * 3
+        values = synth.activations(5, rows, k, device)
+        with B.force_kernel(family):
+            for weight in weights:
+                if op == "dense":
+                    B.mlx_dense_residual_qmv(values, weight)
+                else:
+                    B.mlx_affine_qmv(values, *weight)
         torch.cuda.synchronize()
         ok, words = _lib.device_status()
         print(json.dumps({"capture": spec, "device_status_ok": bool(ok)}))
@@ -1071,7 +1092,7 @@ def main():
     parser.add_argument("--skip-other", action="store_true", help="leave out the other named workloads")
     parser.add_argument("--capture", default=None, metavar="OP:FAMILY:ROWS",
                         help="run a few launches of one operator and exit (a small target for ncu): OP is mlp, "
-                             "swiglu, down or attention (ROWS = sequences); FAMILY is default, mlp_fused, "
+                             "swiglu, down, attention (ROWS = sequences), dense or lm_head; FAMILY is default, mlp_fused, "
                              "mlp_fused_mma, gemv or umma")
     args = parser.parse_args()
     if args.capture:

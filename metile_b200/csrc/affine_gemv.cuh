@@ -91,9 +91,13 @@ affine_gemv_kernel(const uint16_t* x, GemvWeights first, GemvWeights second, con
     const int slot_end = min(slot_begin + slots_per_part, slots_per_row);
     const int team_global = blockIdx.x * teams_per_cta + team;
     const int teams_total = gridDim.x * teams_per_cta;
-    // Every warp of a CTA runs the same number of iterations (the bounds depend on blockIdx only),
-    // so the __syncthreads below are reached by all of them.
-    const int passes = (N + teams_total * rows_per_pass - 1) / (teams_total * rows_per_pass);
+    // A CTA's row blocks (rows_per_pass rows per team) are blockIdx.x, blockIdx.x + gridDim.x, ...: it
+    // runs as many passes as it has blocks that start below N -- not the grid-wide maximum, which at
+    // N = 8192 made most CTAs spend a second pass on clamped rows whose results nobody stores, in a
+    // kernel bound by instruction issue.  Every warp of a CTA runs the same number of iterations (the
+    // bounds depend on blockIdx only), so the __syncthreads below are reached by all of them.
+    const int row_blocks = (N + teams_per_cta * rows_per_pass - 1) / (teams_per_cta * rows_per_pass);
+    const int passes = (int)((unsigned int)(row_blocks - 1 - (int)blockIdx.x) / gridDim.x) + 1;  // the grid has at most row_blocks CTAs
     const int steps = (slots_per_part + 15) >> 4;  // slot iterations per pass (some lanes idle in the last)
 
     struct Weights {
